@@ -1,0 +1,446 @@
+#!/usr/bin/env python
+"""Benchmark of the MoBA attention path: one step = forward + backward of
+`moba_attention` over one batch of seeded synthetic input.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+Prints ONE JSON line (rank 0). With N > 1 it is launched by torchrun, one
+process per GPU; the units (heads / sequences) are sharded across ranks and no
+collective runs inside the op. Workloads:
+
+  target   q,k,v [1,131072,4,64] bf16, block 128, top_k 8 per GPU  (default; weak scaling:
+           a global [1,131072,4N,64] problem with 4 heads per GPU)
+  cfg2     [1,65536,4,64] per GPU
+  gqa      q [1,131072,32,128], k/v 8 heads, KV heads sharded over the GPUs (strong scaling)
+  varlen   262144 packed tokens, 32 sequences, H=16, D=128, sequences sharded (strong scaling)
+  skewed   q [1,524288,32,128], k/v 8 heads, selections concentrated on early blocks (strong)
+  small    [1,8192,4,64], for quick checks and profiler captures
+
+`--impl reference` times the reference algorithm's CPU restatement (oracle/) on
+the host cores for the same workload, on a bounded sample per step.
+"""
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "MoBA fwd+bwd useful TFLOP/s (S=128K bf16, block 128, top_k 8; ms in ms_per_step)"
+H100_REFERENCE_FWD_BWD_MS = 6.181   # results/sm90-h100/data/moba-bwd.csv:9 of the reference (H100, its Triton kernels)
+
+BLOCK, TOPK = 128, 8
+
+
+# ----------------------------------------------------------------------------
+# workloads
+# ----------------------------------------------------------------------------
+
+def varlen_lengths():
+    """32 lengths, log-uniform in [1024, 32768] from seed 1, rounded to 128, sum 262144."""
+    g = torch.Generator().manual_seed(1)
+    u = torch.rand(32, generator=g, dtype=torch.float64)
+    raw = torch.exp(math.log(1024.0) + u * math.log(32.0))
+    scaled = raw * (262144.0 / float(raw.sum()))
+    lens = (torch.round(scaled / 128.0) * 128).to(torch.int64).clamp(min=128)
+    lens[int(lens.argmax())] += 262144 - int(lens.sum())
+    return [int(x) for x in lens]
+
+
+def lpt_partition(costs, parts):
+    """Longest-processing-time assignment; returns a list of index lists."""
+    bins = [[] for _ in range(parts)]
+    load = [0] * parts
+    for i in sorted(range(len(costs)), key=lambda i: -costs[i]):
+        j = load.index(min(load))
+        bins[j].append(i)
+        load[j] += costs[i]
+    return [sorted(b) for b in bins]
+
+
+def describe(name, rank, world):
+    """Per-rank shard of the workload."""
+    if name in ("target", "cfg2", "small"):
+        s = {"target": 131072, "cfg2": 65536, "small": 8192}[name]
+        return dict(name=name, seqlens=[s], hq=4, hkv=4, d=64, packed=False, scaling="weak",
+                    seed=1000 * rank, skew=False,
+                    text=f"[1,{s},4,64] bf16 per GPU (global [1,{s},{4 * world},64], heads sharded), "
+                         f"block {BLOCK}, top_k {TOPK}, fwd+bwd")
+    if name in ("gqa", "skewed"):
+        s = 131072 if name == "gqa" else 524288
+        if 8 % world:
+            raise SystemExit(f"{name}: 8 KV heads do not shard over {world} GPUs")
+        hkv = 8 // world
+        return dict(name=name, seqlens=[s], hq=4 * hkv, hkv=hkv, d=128, packed=False,
+                    scaling="strong", seed=1000 * rank, skew=(name == "skewed"),
+                    text=f"q [1,{s},32,128] k/v 8 heads bf16, KV heads sharded {hkv}/GPU, "
+                         f"block {BLOCK}, top_k {TOPK}, fwd+bwd")
+    if name == "varlen":
+        lens = varlen_lengths()
+        mine = lpt_partition(lens, world)[rank]
+        return dict(name=name, seqlens=[lens[i] for i in mine], hq=16, hkv=16, d=128, packed=True,
+                    scaling="strong", seed=1000 * rank, skew=False,
+                    text=f"262144 packed tokens, 32 sequences (log-uniform 1024..32768, seed 1), H=16, D=128 "
+                         f"bf16, sequences sharded by token count, block {BLOCK}, top_k {TOPK}, fwd+bwd")
+    raise SystemExit(f"unknown workload {name}")
+
+
+def attended_pairs(seq_len):
+    total = 0
+    for pos0 in range(0, seq_len, BLOCK):
+        j, rows = pos0 // BLOCK, min(BLOCK, seq_len - pos0)
+        total += rows * (rows + 1) // 2 + rows * min(j, TOPK - 1) * BLOCK
+    return total
+
+
+def selected_pairs(seq_len):
+    return sum(min(BLOCK, seq_len - p) * (1 + min(p // BLOCK, TOPK - 1)) for p in range(0, seq_len, BLOCK))
+
+
+def gate_candidates(seq_len):
+    return sum(min(BLOCK, seq_len - p) * (p // BLOCK) for p in range(0, seq_len, BLOCK))
+
+
+def accounting(wl):
+    """Algorithmic work of one step on this rank (useful FLOPs, compulsory bytes)."""
+    t = sum(wl["seqlens"])
+    hq, hkv, d = wl["hq"], wl["hkv"], wl["d"]
+    att = sum(attended_pairs(s) for s in wl["seqlens"]) * hq
+    pairs = sum(selected_pairs(s) for s in wl["seqlens"]) * hq
+    cand = sum(gate_candidates(s) for s in wl["seqlens"]) * hq
+    f_fwd = 4.0 * d * att
+    e = 2                                               # bf16
+    qb, kvb = t * hq * d * e, t * hkv * d * e
+    nb_total = sum(-(-s // BLOCK) for s in wl["seqlens"])
+    rows = t * hq
+    return dict(
+        tokens=t, pairs=pairs, f_fwd=f_fwd, f_step=3.5 * f_fwd,
+        bytes_step=(qb + 2 * kvb + qb + rows * 4) + (qb + 2 * kvb + 2 * qb + rows * 4 + qb + 2 * kvb),
+        kernels={
+            "pool_kernel": ("hbm", kvb + nb_total * hkv * d * e),
+            "gate_portable_kernel": ("tensor", 2.0 * d * cand),
+            "gate_sm100_kernel": ("tensor", 2.0 * d * cand),
+            "count_kernel": ("hbm", rows * TOPK * 4),
+            "colscan_kernel": ("hbm", 0),
+            "offsets_order_kernel": ("hbm", nb_total * hkv * 12),
+            "scatter_kernel": ("hbm", rows * TOPK * 4 + pairs * 12),
+            "fill_kernel": ("hbm", rows * TOPK * 4),
+            "fwd_portable_kernel": ("tensor", f_fwd),
+            "fwd_sm100_kernel": ("tensor", f_fwd),
+            "merge_kernel": ("hbm", pairs * (d * e + 4) + rows * TOPK * 4 + qb + rows * 4),
+            "delta_kernel": ("hbm", 2 * qb + rows * 4),
+            "bwd_portable_kernel": ("tensor", 2.5 * f_fwd),
+            "bwd_sm100_kernel": ("tensor", 2.5 * f_fwd),
+            "dq_reduce_kernel": ("hbm", pairs * d * e + rows * TOPK * 4 + qb),
+        })
+
+
+def make_inputs(wl, pinned):
+    """Seeded N(0,1) bf16 tensors from a CPU generator: q, k, v, dO (+cu_seqlens)."""
+    g = torch.Generator().manual_seed(wl["seed"])
+    t, hq, hkv, d = sum(wl["seqlens"]), wl["hq"], wl["hkv"], wl["d"]
+    q = torch.randn((1, t, hq, d), generator=g)
+    k = torch.randn((1, t, hkv, d), generator=g)
+    v = torch.randn((1, t, hkv, d), generator=g)
+    do = torch.randn((1, t, hq, d), generator=g)
+    if wl["skew"]:
+        g2 = torch.Generator().manual_seed(2 + wl["seed"])
+        n = torch.randn((hkv, d), generator=g2)
+        u = 2.0 * n / n.norm(dim=-1, keepdim=True)
+        q += u.repeat_interleave(hq // hkv, dim=0)[None, None]
+        k[:, : t // 10] += u[None, None]
+    out = [x.to(torch.bfloat16) for x in (q, k, v, do)]
+    if pinned:
+        out = [x.pin_memory() for x in out]
+    cu = None
+    if wl["packed"]:
+        cu = torch.tensor([0] + list(torch.tensor(wl["seqlens"]).cumsum(0)), dtype=torch.int32)
+    return out, cu
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm=float(p["hbm_gbs"]), tensor=float(p["bf16_tflops_sustained"]),
+                    tensor_burst=float(p["bf16_tflops"]), source="measured")
+    return dict(hbm=6650.0, tensor=1400.0, tensor_burst=1590.0, source="fallback")
+
+
+# ----------------------------------------------------------------------------
+# clocks
+# ----------------------------------------------------------------------------
+
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu, self.proc = gpu_index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            text, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            text, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        for line in text.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9 or not f[1].isdigit():
+                continue
+            sm.append(int(f[1])); mx.append(int(f[2]))
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ----------------------------------------------------------------------------
+# CPU baseline (oracle) -- the only place this file touches oracle/
+# ----------------------------------------------------------------------------
+
+def cpu_sample(wl, sample_tokens):
+    """One pass of the oracle over the first `sample_tokens` tokens of head 0 of the
+    first sequence: gate + sparse forward + backward in float32 on all host threads."""
+    from oracle import moba_oracle as orc
+    s = min(sample_tokens, wl["seqlens"][0])
+    g = torch.Generator().manual_seed(wl["seed"])
+    d = wl["d"]
+    q, k, v, do = (torch.randn((1, s, 1, d), generator=g).to(torch.bfloat16) for _ in range(4))
+    t0 = time.perf_counter()
+    mask = orc.selection_mask(q, k, BLOCK, TOPK)
+    idx = orc.mask_to_block_idx(mask, TOPK)
+    orc.attention_sparse(q, k, v, BLOCK, idx, dout=do, compute_dtype=torch.float32, row_chunk=1024)
+    dt = time.perf_counter() - t0
+    flops = 3.5 * 4.0 * d * attended_pairs(s)
+    return flops, dt, f"first {s} tokens of one head ([1,{s},1,{d}]), gate + fwd + bwd, float32"
+
+
+def run_reference(args, wl, rank, world):
+    if rank != 0:
+        return
+    flops = secs = 0.0
+    what = ""
+    for i in range(args.warmup + args.steps):
+        f, dt, what = cpu_sample(wl, 16384)
+        if i >= args.warmup:
+            flops += f; secs += dt
+    val = flops / secs / 1e12
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * secs / args.steps,
+        "higher_is_better": True, "scaling": wl["scaling"], "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": wl["text"], "sample_per_step": what},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": what},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "reference checkout is not present on the GPU machine; oracle/ is its CPU restatement, "
+                "pinned to the reference's own oracle by tests/golden",
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------
+# our arm
+# ----------------------------------------------------------------------------
+
+def run_ours(args, wl, rank, world, local_rank):
+    import moba_triton_b200 as moba
+    from moba_triton_b200 import _lib
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+    if args.path:
+        _lib.set_kernel_path({"portable": _lib.PATH_PORTABLE, "tcgen05": _lib.PATH_TCGEN05}[args.path])
+
+    cfg = moba.MoBAConfig(block_size=BLOCK, top_k=TOPK)
+    acct = accounting(wl)
+    host, cu = make_inputs(wl, pinned=True)
+    cu_dev = None if cu is None else cu.to(dev)
+    max_seqlen = max(wl["seqlens"]) if wl["packed"] else None
+    kw = dict(cu_seqlens=cu_dev, max_seqlen=max_seqlen) if wl["packed"] else {}
+
+    q, k, v, do = (x.to(dev) for x in host)
+    q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
+
+    def step():
+        q.grad = k.grad = v.grad = None
+        out = moba.moba_attention(q, k, v, cfg, **kw)
+        out.backward(do)
+        return out
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        barrier()
+        ms = a.elapsed_time(b)
+        if dist is not None:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t)
+        return ms
+
+    for _ in range(args.warmup):
+        step()
+    clocks = ClockSampler(local_rank)
+    clocks.start()
+    launches0 = _lib.launch_count()
+    ms_total = timed(step, args.steps)
+    launches = _lib.launch_count() - launches0
+    clock_info = clocks.stop()
+    ms_step = ms_total / args.steps
+
+    # forward only (inference entry point)
+    with torch.no_grad():
+        fwd = lambda: moba.moba_forward(q, k, v, cfg, **kw)
+        for _ in range(2):
+            fwd()
+        ms_fwd = timed(fwd, max(2, args.steps // 2)) / max(2, args.steps // 2)
+
+    # end to end: host buffers in, host buffers out, through the public API
+    outs_host = [torch.empty_like(h).pin_memory() for h in (host[0], host[0], host[1], host[2])]
+
+    def e2e_step():
+        qd, kd, vd, dod = (h.to(dev, non_blocking=True) for h in host)
+        qd.requires_grad_(True); kd.requires_grad_(True); vd.requires_grad_(True)
+        out = moba.moba_attention(qd, kd, vd, cfg, **kw)
+        out.backward(dod)
+        for dst, src in zip(outs_host, (out.detach(), qd.grad, kd.grad, vd.grad)):
+            dst.copy_(src, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    e2e_step()
+    ms_e2e = timed(e2e_step, e2e_steps) / e2e_steps
+    h2d = sum(h.numel() * h.element_size() for h in host)
+    d2h = sum(h.numel() * h.element_size() for h in outs_host)
+
+    # per-kernel durations (CUDA events on the launching stream, inside the library)
+    _lib.profile(True)
+    prof_steps = 3
+    for _ in range(prof_steps):
+        step()
+    torch.cuda.synchronize()
+    _lib.profile(False)
+    table = _lib.profile_read()
+
+    total_f = acct["f_step"]
+    total_tokens = acct["tokens"]
+    if dist is not None:
+        t = torch.tensor([total_f, float(total_tokens)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t)
+        total_f, total_tokens = float(t[0]), int(t[1])
+    pk = peaks()
+
+    if rank == 0:
+        kernels = {n: {"launches_per_step": c / prof_steps, "ms_per_launch": ms / c,
+                       "share": ms / max(1e-9, sum(m for _, m in table.values()))}
+                   for n, (c, ms) in sorted(table.items(), key=lambda kv: -kv[1][1])}
+        top = next(iter(kernels))
+        kind, amount = acct["kernels"].get(top, ("tensor", 0.0))
+        dur_s = kernels[top]["ms_per_launch"] * 1e-3
+        if kind == "tensor":
+            achieved, peak, unit = amount / dur_s / 1e12, pk["tensor"], "TFLOP/s"
+        else:
+            achieved, peak, unit = amount / dur_s / 1e9, pk["hbm"], "GB/s"
+        traffic = None
+        tpath = os.path.join(ROOT, "profiles", "traffic.json")
+        if os.path.exists(tpath):
+            traffic = json.load(open(tpath)).get(wl["name"], {}).get(top)
+        t_roof = max(acct["f_step"] / (pk["tensor_burst"] * 1e12), acct["bytes_step"] / (pk["hbm"] * 1e9))
+        line = {
+            "metric": METRIC, "value": total_f / (ms_step * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": wl["scaling"],
+            "vs_baseline": (H100_REFERENCE_FWD_BWD_MS / ms_step) if wl["name"] == "target" else None,
+            "vs_baseline_note": "reference Triton kernels on H100, fwd+bwd at [1,131072,4,64]: 6.181 ms; "
+                                "the reference publishes no B200 number",
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": wl["text"], "l2": "inputs per step (q,k,v,dO >= 268 MB) exceed the 126 MB L2; no flush",
+                       "tokens_all_gpus": total_tokens, "kernel_path": args.path or "auto"},
+            "fwd_ms": ms_fwd, "fwd_tflops": acct["f_fwd"] / (ms_fwd * 1e-3) / 1e12,
+            "op_roofline": {"t_roof_ms": t_roof * 1e3, "frac": t_roof * 1e3 / ms_step,
+                            "peak": f"{pk['tensor_burst']} TFLOP/s burst, {pk['hbm']} GB/s ({pk['source']})"},
+            "e2e": {"value": total_f / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches,
+            "clocks": clock_info,
+            "roofline": {"kernel": top, "bound": kind, "achieved": achieved, "peak": peak, "unit": unit,
+                         "frac": achieved / peak, "traffic": traffic,
+                         "peak_source": f"{pk['source']} ({'sustained' if kind == 'tensor' else 'copy'})"},
+            "kernels": kernels,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            f, dt, what = cpu_sample(wl, 65536)
+            line["cpu_baseline"] = {"value": f / dt / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+                                    "kind": "port", "sample": what, "seconds": dt}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="target")
+    ap.add_argument("--path", default="", choices=["", "portable", "tcgen05"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torchrun --nproc-per-node N for --gpus N")
+    wl = describe(args.workload, rank, world)
+    if args.impl == "reference":
+        run_reference(args, wl, rank, world)
+    else:
+        run_ours(args, wl, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

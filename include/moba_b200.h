@@ -1,0 +1,162 @@
+/*
+ * moba_b200.h -- C ABI of the B200 (sm_100a) MoBA attention engine.
+ *
+ * Every entry point takes plain device pointers, a problem description and a
+ * CUDA stream (passed as void*, a cudaStream_t). Nothing here allocates,
+ * synchronises with the host or throws: the caller owns every buffer, work is
+ * enqueued on the given stream, and the return value is 0 on success or a
+ * negative MOBA_B200_E* code (text via moba_b200_last_error()).
+ *
+ * Each declaration names the reference function it stands in for, by the path
+ * inside the ZuricZ/moba-triton checkout.
+ *
+ * Layouts (all contiguous):
+ *   q, out, dout, dq      [B, S, Hq,  D]   (packed: [1, T, Hq, D])
+ *   k, v, dk, dv          [B, S, Hkv, D]
+ *   kbar                  [n_seq, Hkv, num_blocks, D]          dtype of k
+ *   block_idx             [B, Hq, S, slots] int32, ascending ids, -1 padded,
+ *                         ids local to the sequence
+ *   col_nnz, order        [n_seq, Hkv, num_blocks]   int32
+ *   col_offsets           [n_seq, Hkv, num_blocks+1] int32
+ *   row/head/slot arrays  [n_seq, Hkv, capacity]     int32,
+ *                         capacity = (Hq/Hkv) * max_seqlen * slots
+ *   part_o                [B, Hq, S, slots, D]  (dtype of q, or float32)
+ *   part_lse, dq marker   [B, Hq, S, slots]     float32, log2 units, -inf = unwritten
+ *   lse, delta            [B, Hq, S]            float32 (lse in log2 units)
+ *   dq_part               [B, Hq, S, slots, D]  dtype of q
+ */
+#ifndef MOBA_B200_H_
+#define MOBA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MOBA_B200_ABI_VERSION 1
+
+enum { MOBA_B200_F32 = 0, MOBA_B200_BF16 = 1, MOBA_B200_F16 = 2 };
+
+enum {
+  MOBA_B200_OK = 0,
+  MOBA_B200_EINVAL = -1,      /* bad argument (shape, dtype, null pointer) */
+  MOBA_B200_EUNSUPPORTED = -2,/* valid request this build has no kernel for */
+  MOBA_B200_ECUDA = -3,       /* a CUDA call failed; see last_error */
+  MOBA_B200_ESCRATCH = -4     /* scratch buffer too small */
+};
+
+/* Kernel family selection. AUTO picks TCGEN05 whenever the shape allows. */
+enum { MOBA_B200_PATH_AUTO = 0, MOBA_B200_PATH_PORTABLE = 1, MOBA_B200_PATH_TCGEN05 = 2 };
+
+/* Stages, for moba_b200_path_for(). */
+enum { MOBA_B200_STAGE_GATE = 0, MOBA_B200_STAGE_FWD = 1, MOBA_B200_STAGE_BWD = 2 };
+
+typedef struct moba_b200_problem {
+  int32_t dtype;          /* MOBA_B200_F32 / BF16 / F16: dtype of q, k, v */
+  int32_t batch;          /* B of q/k/v; 1 when packed */
+  int32_t tokens;         /* S (padded) or T (packed total) */
+  int32_t n_seq;          /* B, or the number of packed sequences */
+  int32_t max_seqlen;     /* S, or the longest packed sequence */
+  int32_t q_heads;
+  int32_t kv_heads;       /* divides q_heads */
+  int32_t head_dim;       /* power of two, row >= 128 bytes */
+  int32_t block_size;     /* >= 16 */
+  int32_t top_k;
+  int32_t slots;          /* selections a query can hold: take + always_current */
+  int32_t take;           /* past blocks ranked in per query */
+  int32_t always_current; /* 1: the query's own block is always attended */
+  int32_t num_blocks;     /* cdiv(max_seqlen, block_size) */
+  int32_t causal;         /* 1: mask future keys inside the own block */
+  int32_t packed;         /* 1: cu_seqlens describes the token axis */
+  int32_t path;           /* MOBA_B200_PATH_* */
+  int32_t part_f32;       /* 1: part_o is float32 instead of the dtype of q */
+} moba_b200_problem;
+
+typedef struct moba_b200_index {
+  const int32_t* col_nnz;
+  const int32_t* col_offsets;
+  const int32_t* order;
+  const int32_t* row_indices;
+  const int32_t* head_indices;
+  const int32_t* slot_of_pair;
+  int64_t capacity;       /* entries per (sequence, kv head) in the three pair arrays */
+} moba_b200_index;
+
+/* ABI version of the loaded library (compare with MOBA_B200_ABI_VERSION). */
+int moba_b200_abi_version(void);
+
+/* Text of the calling thread's most recent failure; never NULL. */
+const char* moba_b200_last_error(void);
+
+/* Kernels launched by this library since it was loaded (all threads). */
+long long moba_b200_launch_count(void);
+
+/* Measurement aid: when enabled, every kernel launch of the library is
+ * bracketed by CUDA events on its stream (returns the previous setting).
+ * moba_b200_profile_read waits for the recorded launches, writes one
+ * "kernel_name launches total_ms" line per kernel into buf (NUL terminated,
+ * at most cap bytes), clears the record and returns the text length.
+ * No counterpart in the reference (it times stages from Python,
+ * bench/stages.py). */
+int moba_b200_profile_enable(int on);
+int moba_b200_profile_read(char* buf, size_t cap);
+
+/* Which kernel family (MOBA_B200_PATH_PORTABLE or _TCGEN05) a stage would run
+ * for this problem, or a negative error code. */
+int moba_b200_path_for(const moba_b200_problem* p, int stage);
+
+/* Bytes of scratch moba_b200_transpose needs for this problem. */
+size_t moba_b200_transpose_scratch_bytes(const moba_b200_problem* p);
+
+/* Mean key of every block.
+ * Replaces pool_blocks / pool_blocks_kernel (src/moba/kernels/pooling.py:25-163). */
+int moba_b200_pool(const moba_b200_problem* p, const void* k, const int32_t* cu_seqlens,
+                   void* kbar, void* stream);
+
+/* Scores every query against the block means of its past blocks, keeps the
+ * best `take` (ties to the lower id), adds the own block, emits ascending ids.
+ * Replaces gate_select / gate_kernel (src/moba/kernels/gating.py:92-448). */
+int moba_b200_gate(const moba_b200_problem* p, const void* q, const void* kbar,
+                   const int32_t* cu_seqlens, int32_t* block_idx, void* stream);
+
+/* CSR -> CSC regrouping of the selections by (sequence, kv head, block):
+ * histogram, prefix scan (+ longest-first order), stable scatter.
+ * Replaces build_csc_from_indices and its three kernels
+ * (src/moba/kernels/routing.py:138-427). */
+int moba_b200_transpose(const moba_b200_problem* p, const int32_t* block_idx,
+                        const int32_t* cu_seqlens, int32_t* col_nnz, int32_t* col_offsets,
+                        int32_t* order, int32_t* row_indices, int32_t* head_indices,
+                        int32_t* slot_of_pair, void* scratch, size_t scratch_bytes,
+                        void* stream);
+
+/* KV-block-major attention: one K/V block resident per CTA, the queries that
+ * selected it gathered through the index; writes normalised partial outputs and
+ * their log2-sum-exp per (query, slot). Resets part_lse to -inf first.
+ * Replaces attend_partials / moba_fwd_kernel (src/moba/kernels/moba_fwd.py:229-425,566-665). */
+int moba_b200_fwd(const moba_b200_problem* p, const void* q, const void* k, const void* v,
+                  const moba_b200_index* index, const int32_t* cu_seqlens,
+                  void* part_o, float* part_lse, void* stream);
+
+/* Merges a query's partials: LSE = log2 sum 2^lse_i, O = sum 2^(lse_i-LSE) O_i.
+ * lse may be NULL. Unwritten slots (part_lse == -inf) are skipped by selection,
+ * never by multiplication. Replaces combine_partials / moba_combine_kernel
+ * (src/moba/kernels/moba_fwd.py:428-521,668-725). */
+int moba_b200_merge(const moba_b200_problem* p, const void* part_o, const float* part_lse,
+                    void* out, float* lse, void* stream);
+
+/* Backward: delta = rowsum(out*dout); per KV block dK/dV owned by one CTA and
+ * stored once (zeros for unselected blocks); dQ written as per-(query, slot)
+ * partials and summed in slot order. `part_lse` is the forward's buffer, used
+ * as the written-slot marker. Replaces compute_delta, moba_backward /
+ * moba_bwd_kernel and reduce_dq (src/moba/kernels/moba_bwd.py:134-160,215-579). */
+int moba_b200_bwd(const moba_b200_problem* p, const void* q, const void* k, const void* v,
+                  const void* out, const void* dout, const float* lse, const float* part_lse,
+                  const moba_b200_index* index, const int32_t* cu_seqlens,
+                  float* delta, void* dq_part, void* dq, void* dk, void* dv, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOBA_B200_H_ */

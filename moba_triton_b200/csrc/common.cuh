@@ -1,0 +1,133 @@
+// Shared declarations for the MoBA sm_100a engine: the problem record, dtype
+// traits, error plumbing and the launch functions each translation unit exports
+// to api.cu.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/moba_b200.h"
+
+namespace moba {
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+void set_error(const char* fmt, ...);
+
+#define MOBA_CUDA_OK(expr)                                                        \
+  do {                                                                            \
+    cudaError_t e__ = (expr);                                                     \
+    if (e__ != cudaSuccess) {                                                     \
+      ::moba::set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), \
+                        __FILE__, __LINE__);                                      \
+      return MOBA_B200_ECUDA;                                                     \
+    }                                                                             \
+  } while (0)
+
+// Counts every kernel launch of the library and, when profiling is switched on
+// through moba_b200_profile_enable(), brackets it with CUDA events on its stream.
+struct KernelTimer {
+  KernelTimer(const char* name, cudaStream_t st);
+  ~KernelTimer();
+  const char* name_;
+  cudaStream_t st_;
+  cudaEvent_t start_;
+  bool on_;
+};
+
+#define MOBA_LAUNCH_OK(what)                                                      \
+  do {                                                                            \
+    cudaError_t e__ = cudaGetLastError();                                         \
+    if (e__ != cudaSuccess) {                                                     \
+      ::moba::set_error("launch of %s failed: %s", what, cudaGetErrorString(e__));\
+      return MOBA_B200_ECUDA;                                                     \
+    }                                                                             \
+  } while (0)
+
+// ---- element types -------------------------------------------------------
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+  static __device__ __forceinline__ float to_f(float x) { return x; }
+  static __device__ __forceinline__ float from_f(float x) { return x; }
+  static __device__ __forceinline__ float round_f(float x) { return x; }
+};
+template <> struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 x) { return __bfloat162float(x); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float x) { return __float2bfloat16_rn(x); }
+  static __device__ __forceinline__ float round_f(float x) {
+    return __bfloat162float(__float2bfloat16_rn(x));
+  }
+};
+template <> struct Elem<__half> {
+  static __device__ __forceinline__ float to_f(__half x) { return __half2float(x); }
+  static __device__ __forceinline__ __half from_f(float x) { return __float2half_rn(x); }
+  static __device__ __forceinline__ float round_f(float x) {
+    return __half2float(__float2half_rn(x));
+  }
+};
+
+static inline size_t dtype_size(int dtype) { return dtype == MOBA_B200_F32 ? 4 : 2; }
+
+// Sequence geometry shared by every kernel: where sequence `seq` starts on the
+// token axis and how long it is. Padded batches have n_seq == batch and every
+// sequence is `tokens` long; packed batches read cu_seqlens.
+struct SeqSpan {
+  int bos;   // first token (index on the token axis of its batch row)
+  int len;   // tokens in the sequence
+};
+__device__ __forceinline__ SeqSpan seq_span(const int32_t* cu, int packed, int seq, int tokens) {
+  SeqSpan s;
+  if (packed) {
+    s.bos = cu[seq];
+    s.len = cu[seq + 1] - s.bos;
+  } else {
+    s.bos = 0;
+    s.len = tokens;
+  }
+  return s;
+}
+
+// ---- stage launchers (defined one per .cu file) -----------------------------
+int launch_pool(const moba_b200_problem& p, const void* k, const int32_t* cu, void* kbar,
+                cudaStream_t st);
+int launch_gate_portable(const moba_b200_problem& p, const void* q, const void* kbar,
+                         const int32_t* cu, int32_t* block_idx, cudaStream_t st);
+int launch_gate_sm100(const moba_b200_problem& p, const void* q, const void* kbar,
+                      const int32_t* cu, int32_t* block_idx, cudaStream_t st);
+bool gate_sm100_supported(const moba_b200_problem& p);
+
+size_t transpose_scratch_bytes(const moba_b200_problem& p);
+int launch_transpose(const moba_b200_problem& p, const int32_t* block_idx, const int32_t* cu,
+                     int32_t* col_nnz, int32_t* col_offsets, int32_t* order, int32_t* rows,
+                     int32_t* heads, int32_t* slots, void* scratch, size_t scratch_bytes,
+                     cudaStream_t st);
+
+int launch_fill_lse(const moba_b200_problem& p, float* part_lse, cudaStream_t st);
+int launch_fwd_portable(const moba_b200_problem& p, const void* q, const void* k, const void* v,
+                        const moba_b200_index& ix, const int32_t* cu, void* part_o,
+                        float* part_lse, cudaStream_t st);
+int launch_fwd_sm100(const moba_b200_problem& p, const void* q, const void* k, const void* v,
+                     const moba_b200_index& ix, const int32_t* cu, void* part_o,
+                     float* part_lse, cudaStream_t st);
+bool fwd_sm100_supported(const moba_b200_problem& p);
+int launch_merge(const moba_b200_problem& p, const void* part_o, const float* part_lse,
+                 void* out, float* lse, cudaStream_t st);
+
+int launch_delta(const moba_b200_problem& p, const void* out, const void* dout, float* delta,
+                 cudaStream_t st);
+int launch_bwd_portable(const moba_b200_problem& p, const void* q, const void* k, const void* v,
+                        const void* dout, const float* lse, const float* delta,
+                        const moba_b200_index& ix, const int32_t* cu, void* dq_part, void* dk,
+                        void* dv, cudaStream_t st);
+int launch_bwd_sm100(const moba_b200_problem& p, const void* q, const void* k, const void* v,
+                     const void* dout, const float* lse, const float* delta,
+                     const moba_b200_index& ix, const int32_t* cu, void* dq_part, void* dk,
+                     void* dv, cudaStream_t st);
+bool bwd_sm100_supported(const moba_b200_problem& p);
+int launch_dq_reduce(const moba_b200_problem& p, const void* dq_part, const float* part_lse,
+                     void* dq, cudaStream_t st);
+
+}  // namespace moba

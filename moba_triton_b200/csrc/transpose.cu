@@ -1,0 +1,261 @@
+// Transpose: regroups per-query selections (CSR, block_idx) by key/value block
+// (CSC) with a *stable* counting sort, so a column lists its queries ordered by
+// (query head, row) on every run.
+//
+//   1. count    one CTA per (row chunk, sequence, query head): shared-memory
+//               histogram over blocks -> tile_counts[seq,kvh][block][g*C + chunk]
+//   2. colscan  one warp per (sequence, kv head, block): exclusive scan of that
+//               block's tile counts in (g, chunk) order; total -> col_nnz
+//   3. offsets  one CTA per (sequence, kv head): exclusive scan over blocks ->
+//               col_offsets, and the longest-first dispatch order (stable
+//               descending sort of col_nnz, by rank counting)
+//   4. scatter  one warp per (row chunk, sequence, query head): walks its rows in
+//               order, ranks equal blocks inside the warp with match.any and
+//               writes (row, head, slot) at cursor[block]++.
+//
+// Stands in for count_columns_kernel / offsets_and_order_kernel /
+// scatter_pairs_kernel of the reference (src/moba/kernels/routing.py:138-301),
+// which claim positions with an atomic cursor and therefore leave the order
+// inside a column to the scheduler.
+#include "common.cuh"
+
+namespace moba {
+
+struct TransposeGeom {
+  int chunk_rows;   // R, a power of two
+  int chunks;       // C = cdiv(max_seqlen, R)
+};
+static inline TransposeGeom transpose_geom(const moba_b200_problem& p) {
+  int r = 256;
+  while ((p.max_seqlen + r - 1) / r > 256) r <<= 1;
+  return TransposeGeom{r, (p.max_seqlen + r - 1) / r};
+}
+size_t transpose_scratch_bytes(const moba_b200_problem& p) {
+  const TransposeGeom g = transpose_geom(p);
+  const size_t group = p.q_heads / p.kv_heads;
+  return (size_t)p.n_seq * p.kv_heads * p.num_blocks * group * g.chunks * sizeof(int32_t);
+}
+
+__device__ __forceinline__ size_t block_idx_row(const moba_b200_problem& p, int seq, int hq,
+                                                int bos, int row) {
+  const size_t b = p.packed ? 0 : (size_t)seq;
+  return ((b * p.q_heads + hq) * p.tokens + bos + row) * (size_t)p.slots;
+}
+
+__global__ void __launch_bounds__(256)
+count_kernel(const int32_t* __restrict__ block_idx, const int32_t* __restrict__ cu,
+             int32_t* __restrict__ tile_counts, moba_b200_problem p, int R, int C) {
+  extern __shared__ int hist[];
+  const int chunk = blockIdx.x;
+  const int seq = blockIdx.y / p.q_heads, hq = blockIdx.y % p.q_heads;
+  const SeqSpan sp = seq_span(cu, p.packed, seq, p.tokens);
+  const int row0 = chunk * R;
+  if (row0 >= sp.len) return;
+  const int rows = min(R, sp.len - row0);
+  const int nb_lim = (row0 + rows - 1) / p.block_size + 1;
+  for (int i = threadIdx.x; i < nb_lim; i += 256) hist[i] = 0;
+  __syncthreads();
+  const int32_t* src = block_idx + block_idx_row(p, seq, hq, sp.bos, row0);
+  const int n = rows * p.slots;
+  for (int e = threadIdx.x; e < n; e += 256) {
+    const int blk = src[e];
+    if (blk >= 0 && blk < nb_lim) atomicAdd(&hist[blk], 1);
+  }
+  __syncthreads();
+  const int group = p.q_heads / p.kv_heads;
+  const int kvh = hq / group, g = hq % group;
+  int32_t* dst = tile_counts + ((size_t)(seq * p.kv_heads + kvh) * p.num_blocks) * (group * C) + g * C + chunk;
+  for (int i = threadIdx.x; i < nb_lim; i += 256) dst[(size_t)i * (group * C)] = hist[i];
+}
+
+// One warp per column. Replaces the column's tile counts by their exclusive
+// prefix (in (g, chunk) order) and writes the column total.
+__global__ void __launch_bounds__(128)
+colscan_kernel(const int32_t* __restrict__ cu, int32_t* __restrict__ tile_counts,
+               int32_t* __restrict__ col_nnz, moba_b200_problem p, int R, int C) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col = blockIdx.x * 4 + warp;
+  if (col >= p.num_blocks) return;
+  const int seq = blockIdx.y / p.kv_heads;
+  const SeqSpan sp = seq_span(cu, p.packed, seq, p.tokens);
+  int32_t* out_nnz = col_nnz + (size_t)blockIdx.y * p.num_blocks + col;
+  if ((size_t)col * p.block_size >= (size_t)sp.len) {
+    if (lane == 0) *out_nnz = 0;
+    return;
+  }
+  const int group = p.q_heads / p.kv_heads;
+  const int c_lo = (int)(((size_t)col * p.block_size) / R);
+  const int c_hi = (sp.len + R - 1) / R;                    // exclusive
+  const int span = c_hi - c_lo;
+  int32_t* base = tile_counts + ((size_t)blockIdx.y * p.num_blocks + col) * (group * C);
+  int running = 0;
+  const int total = group * span;
+  for (int i0 = 0; i0 < total; i0 += 32) {
+    const int i = i0 + lane;
+    int v = 0;
+    int32_t* ptr = nullptr;
+    if (i < total) {
+      ptr = base + (i / span) * C + c_lo + (i % span);
+      v = *ptr;
+    }
+    int incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    if (ptr) *ptr = running + incl - v;
+    running += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  if (lane == 0) *out_nnz = running;
+}
+
+// One CTA per (sequence, kv head): col_offsets and the dispatch order.
+__global__ void __launch_bounds__(1024)
+offsets_order_kernel(const int32_t* __restrict__ col_nnz, int32_t* __restrict__ col_offsets,
+                     int32_t* __restrict__ order, int nb) {
+  extern __shared__ int cnt[];              // [nb]
+  __shared__ int warp_sums[32];
+  __shared__ int carry_s;
+  const int32_t* nnz = col_nnz + (size_t)blockIdx.x * nb;
+  int32_t* off = col_offsets + (size_t)blockIdx.x * (nb + 1);
+  int32_t* ord = order + (size_t)blockIdx.x * nb;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) carry_s = 0;
+  __syncthreads();
+  for (int i0 = 0; i0 < nb; i0 += 1024) {
+    const int i = i0 + threadIdx.x;
+    const int v = (i < nb) ? nnz[i] : 0;
+    if (i < nb) cnt[i] = v;
+    int incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      int w = warp_sums[lane];
+      int wi = w;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, wi, o);
+        if (lane >= o) wi += t;
+      }
+      warp_sums[lane] = wi - w;             // exclusive over warps
+    }
+    __syncthreads();
+    const int carry = carry_s;
+    if (i < nb) off[i] = carry + warp_sums[warp] + incl - v;
+    __syncthreads();
+    if (threadIdx.x == 1023) carry_s = carry + warp_sums[warp] + incl;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) off[nb] = carry_s;
+  // stable descending rank: position of column i = #{j : n_j > n_i or (n_j == n_i and j < i)}
+  for (int i = threadIdx.x; i < nb; i += 1024) {
+    const int ni = cnt[i];
+    int rank = 0;
+    for (int j = 0; j < nb; ++j) {
+      const int nj = cnt[j];
+      rank += (nj > ni || (nj == ni && j < i)) ? 1 : 0;
+    }
+    ord[rank] = i;
+  }
+}
+
+// One warp per (row chunk, sequence, query head).
+__global__ void __launch_bounds__(32)
+scatter_kernel(const int32_t* __restrict__ block_idx, const int32_t* __restrict__ cu,
+               const int32_t* __restrict__ tile_prefix, const int32_t* __restrict__ col_offsets,
+               int32_t* __restrict__ rows_out, int32_t* __restrict__ heads_out,
+               int32_t* __restrict__ slots_out, moba_b200_problem p, int R, int C,
+               long long capacity) {
+  extern __shared__ int cursor[];
+  const int chunk = blockIdx.x;
+  const int seq = blockIdx.y / p.q_heads, hq = blockIdx.y % p.q_heads;
+  const SeqSpan sp = seq_span(cu, p.packed, seq, p.tokens);
+  const int row0 = chunk * R;
+  if (row0 >= sp.len) return;
+  const int rows = min(R, sp.len - row0);
+  const int nb_lim = (row0 + rows - 1) / p.block_size + 1;
+  const int group = p.q_heads / p.kv_heads;
+  const int kvh = hq / group, g = hq % group;
+  const size_t kv_row = (size_t)seq * p.kv_heads + kvh;
+  const int lane = threadIdx.x;
+  const int32_t* pre = tile_prefix + (kv_row * p.num_blocks) * (group * C) + g * C + chunk;
+  const int32_t* off = col_offsets + kv_row * (p.num_blocks + 1);
+  for (int i = lane; i < nb_lim; i += 32) cursor[i] = off[i] + pre[(size_t)i * (group * C)];
+  __syncwarp();
+  const int32_t* src = block_idx + block_idx_row(p, seq, hq, sp.bos, row0);
+  int32_t* ro = rows_out + kv_row * capacity;
+  int32_t* ho = heads_out + kv_row * capacity;
+  int32_t* so = slots_out + kv_row * capacity;
+  const int n = rows * p.slots;
+  const unsigned lt = (1u << lane) - 1u;
+  for (int e0 = 0; e0 < n; e0 += 32) {
+    const int e = e0 + lane;
+    int blk = -1;
+    if (e < n) blk = src[e];
+    const bool valid = blk >= 0 && blk < nb_lim;
+    const int key = valid ? blk : (0x40000000 + lane);
+    const unsigned same = __match_any_sync(0xffffffffu, key);
+    int base = 0;
+    if (valid) base = cursor[blk];
+    __syncwarp();
+    if (valid && (same & lt) == 0) cursor[blk] = base + __popc(same);
+    __syncwarp();
+    if (valid) {
+      const long long dst = base + __popc(same & lt);
+      if (dst < capacity) {
+        ro[dst] = sp.bos + row0 + e / p.slots;
+        ho[dst] = hq;
+        so[dst] = e % p.slots;
+      }
+    }
+  }
+}
+
+int launch_transpose(const moba_b200_problem& p, const int32_t* block_idx, const int32_t* cu,
+                     int32_t* col_nnz, int32_t* col_offsets, int32_t* order, int32_t* rows,
+                     int32_t* heads, int32_t* slots, void* scratch, size_t scratch_bytes,
+                     cudaStream_t st) {
+  const TransposeGeom g = transpose_geom(p);
+  if (scratch_bytes < transpose_scratch_bytes(p)) {
+    set_error("transpose: scratch has %zu bytes, needs %zu", scratch_bytes,
+              transpose_scratch_bytes(p));
+    return MOBA_B200_ESCRATCH;
+  }
+  const size_t hist_bytes = (size_t)p.num_blocks * sizeof(int);
+  if (hist_bytes > 160 * 1024) {
+    set_error("transpose: %d blocks per sequence exceed the shared-memory histogram", p.num_blocks);
+    return MOBA_B200_EUNSUPPORTED;
+  }
+  int32_t* tiles = static_cast<int32_t*>(scratch);
+  const int group = p.q_heads / p.kv_heads;
+  const long long capacity = (long long)group * p.max_seqlen * p.slots;
+  if (hist_bytes > 48 * 1024) {
+    MOBA_CUDA_OK(cudaFuncSetAttribute(count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hist_bytes));
+    MOBA_CUDA_OK(cudaFuncSetAttribute(scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hist_bytes));
+    MOBA_CUDA_OK(cudaFuncSetAttribute(offsets_order_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hist_bytes));
+  }
+  dim3 grid_rows(g.chunks, p.n_seq * p.q_heads);
+  { KernelTimer t__("count_kernel", st);
+  count_kernel<<<grid_rows, 256, hist_bytes, st>>>(block_idx, cu, tiles, p, g.chunk_rows, g.chunks);
+  MOBA_LAUNCH_OK("count_kernel"); }
+  dim3 grid_cols((p.num_blocks + 3) / 4, p.n_seq * p.kv_heads);
+  { KernelTimer t__("colscan_kernel", st);
+  colscan_kernel<<<grid_cols, 128, 0, st>>>(cu, tiles, col_nnz, p, g.chunk_rows, g.chunks);
+  MOBA_LAUNCH_OK("colscan_kernel"); }
+  { KernelTimer t__("offsets_order_kernel", st);
+  offsets_order_kernel<<<p.n_seq * p.kv_heads, 1024, hist_bytes, st>>>(col_nnz, col_offsets, order, p.num_blocks);
+  MOBA_LAUNCH_OK("offsets_order_kernel"); }
+  { KernelTimer t__("scatter_kernel", st);
+  scatter_kernel<<<grid_rows, 32, hist_bytes, st>>>(block_idx, cu, tiles, col_offsets, rows, heads,
+                                                     slots, p, g.chunk_rows, g.chunks, capacity);
+  MOBA_LAUNCH_OK("scatter_kernel"); }
+  return MOBA_B200_OK;
+}
+
+}  // namespace moba

@@ -1,0 +1,150 @@
+"""Forward: KV-block-major attention into per-slot partials, then the merge
+(reference: src/moba/kernels/moba_fwd.py:529-835).
+
+The partials differ from the reference's (m, l, acc) triple: each (query, slot)
+holds the already-normalised output of that one block, `part_o`, and its
+log2-sum-exp, `part_lse`. The merged output and the global log-sum-exp are the
+same quantities. `combine_partials` still accepts the reference's triple.
+"""
+
+from typing import Optional
+
+import torch
+
+from moba_triton_b200 import _lib
+from moba_triton_b200.config import MoBAConfig
+from moba_triton_b200.device import MIN_BLOCK_SIZE, check_gathered_head_dim
+from moba_triton_b200.gqa import head_group_size
+from moba_triton_b200.kernels.routing import CSCIndex, build_csc_fused
+from moba_triton_b200.varlen import validate_cu_seqlens
+
+
+def _validate(q, k, v, cfg: MoBAConfig, cu_seqlens=None, max_seqlen=None) -> None:
+    """Shape / configuration checks before any launch; reads no device memory
+    (reference: moba_fwd.py:733-780, same ValueError wording keys)."""
+    if k.shape != v.shape:
+        raise ValueError(f"key/value shape mismatch: {tuple(k.shape)}, {tuple(v.shape)}")
+    if q.ndim != 4 or k.ndim != 4:
+        raise ValueError(f"shape mismatch: expected [B, S, H, D] tensors, got {tuple(q.shape)}, {tuple(k.shape)}")
+    if q.shape[0] != k.shape[0] or q.shape[1] != k.shape[1] or q.shape[3] != k.shape[3]:
+        raise ValueError(f"shape mismatch: {tuple(q.shape)}, {tuple(k.shape)}, {tuple(v.shape)}")
+    if not (q.dtype == k.dtype == v.dtype):
+        raise ValueError(f"dtype mismatch: {q.dtype}, {k.dtype}, {v.dtype}")
+    _lib.dtype_code(q.dtype)
+    head_group_size(q.shape[2], k.shape[2])
+    if cu_seqlens is not None:
+        if q.shape[0] != 1:
+            raise ValueError(
+                f"packed input must have batch 1, got {q.shape[0]}; every sequence lives on "
+                "the token axis and cu_seqlens says where")
+        if max_seqlen is None:
+            raise ValueError("max_seqlen is required when cu_seqlens is given")
+        validate_cu_seqlens(cu_seqlens, total_tokens=q.shape[1], max_seqlen=max_seqlen)
+    ok, reason = check_gathered_head_dim(q.shape[-1], q.element_size())
+    if not ok:
+        raise ValueError(reason)
+    if cfg.block_size < MIN_BLOCK_SIZE:
+        raise ValueError(
+            f"block_size {cfg.block_size} below the tl.dot minimum of {MIN_BLOCK_SIZE} "
+            "(wording kept from the reference; it is this engine's minimum block too)")
+
+
+def _problem(q, k, cfg, index: CSCIndex, causal=True, part_f32=False):
+    return _lib.make_problem(tuple(q.shape), k.shape[2], q.dtype, cfg, index.cu_seqlens,
+                             index.max_seqlen, causal=causal, part_f32=part_f32)
+
+
+def _check_index(q, k, cfg, index: CSCIndex) -> None:
+    n_seq = index.cu_seqlens.numel() - 1 if index.cu_seqlens is not None else q.shape[0]
+    want = (n_seq, k.shape[2], cfg.num_blocks(index.max_seqlen if index.cu_seqlens is not None else q.shape[1]))
+    if tuple(index.col_nnz.shape) != want or index.num_query_heads != q.shape[2] \
+            or index.max_slots != cfg.slots_per_query:
+        raise ValueError(
+            f"index mismatch: index covers {tuple(index.col_nnz.shape)} columns, "
+            f"{index.num_query_heads} query heads, {index.max_slots} slots; the call needs "
+            f"{want}, {q.shape[2]}, {cfg.slots_per_query}")
+
+
+def empty_partials(shape, slots: int, device, partials_dtype: torch.dtype = torch.float32):
+    """Uninitialised (part_lse [B,H,S,slots] f32, part_o [B,H,S,slots,D]) for a
+    query of `shape` = (B, S, H, D)."""
+    b, s, h, d = shape
+    return (torch.empty((b, h, s, slots), device=device, dtype=torch.float32),
+            torch.empty((b, h, s, slots, d), device=device, dtype=partials_dtype))
+
+
+def attend_partials(q, k, v, cfg: MoBAConfig, index: CSCIndex, causal: bool = True,
+                    partials_dtype: Optional[torch.dtype] = None, partials=None):
+    """Runs the attention stage; returns (part_lse, part_o). `part_lse` is in
+    log2 units and -inf where no block wrote the slot; `part_o` of such a slot
+    is uninitialised."""
+    _lib.require_cuda(q, k, v)
+    _check_index(q, k, cfg, index)
+    if partials_dtype is None:
+        partials_dtype = q.dtype
+    if partials_dtype not in (q.dtype, torch.float32):
+        raise ValueError(f"partials_dtype must be {q.dtype} or float32, got {partials_dtype}")
+    if partials is None:
+        partials = empty_partials(q.shape, index.max_slots, q.device, partials_dtype)
+    part_lse, part_o = partials
+    prob = _problem(q, k, cfg, index, causal, part_o.dtype == torch.float32 and q.dtype != torch.float32)
+    ix = index.c_struct()
+    lib = _lib.load()
+    _lib.check(lib.moba_b200_fwd(prob, _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), ix,
+                                 _lib.ptr(index.cu_seqlens), _lib.ptr(part_o), _lib.ptr(part_lse),
+                                 _lib.stream_ptr(q.device)), "attend_partials")
+    return part_lse, part_o
+
+
+def merge_partials(part_lse, part_o, out_dtype: torch.dtype, return_lse: bool = False):
+    """LSE merge of (part_lse [B,H,S,K], part_o [B,H,S,K,D]) -> O [B,S,H,D]
+    (and lse [B,H,S], log2 units)."""
+    _lib.require_cuda(part_lse, part_o)
+    b, h, s, slots = part_lse.shape
+    d = part_o.shape[-1]
+    if tuple(part_o.shape) != (b, h, s, slots, d):
+        raise ValueError(f"shape mismatch: part_o {tuple(part_o.shape)} against {(b, h, s, slots, d)}")
+    part_lse, part_o = part_lse.contiguous(), part_o.contiguous()
+    out = torch.empty((b, s, h, d), device=part_o.device, dtype=out_dtype)
+    lse = torch.empty((b, h, s), device=part_o.device, dtype=torch.float32) if return_lse else None
+    cfg = MoBAConfig(block_size=16, top_k=slots, always_select_current=False)   # only `slots` matters here
+    prob = _lib.make_problem((b, s, h, d), h, out_dtype, cfg,
+                             part_f32=part_o.dtype == torch.float32 and out_dtype != torch.float32)
+    if part_o.dtype not in (out_dtype, torch.float32):
+        raise ValueError(f"part_o must be {out_dtype} or float32, got {part_o.dtype}")
+    lib = _lib.load()
+    _lib.check(lib.moba_b200_merge(prob, _lib.ptr(part_o), _lib.ptr(part_lse), _lib.ptr(out),
+                                   _lib.ptr(lse), _lib.stream_ptr(out.device)), "combine_partials")
+    return (out, lse) if return_lse else out
+
+
+def combine_partials(part_m, part_l, part_acc, out_dtype: torch.dtype, block_m=None,
+                     return_lse: bool = False):
+    """Reference-signature merge (moba_fwd.py:668-725): takes per-slot maxima,
+    denominators and unnormalised accumulators, with `part_m == -inf` marking an
+    unwritten slot, and feeds them to the merge kernel as (lse, normalised O)."""
+    b, h, s, slots = part_m.shape
+    d = part_acc.shape[-1]
+    if part_l.shape != part_m.shape:
+        raise ValueError(f"shape mismatch: part_l {tuple(part_l.shape)} against part_m {tuple(part_m.shape)}")
+    if tuple(part_acc.shape) != (b, h, s, slots, d):
+        raise ValueError(f"shape mismatch: part_acc {tuple(part_acc.shape)} against {(b, h, s, slots, d)}")
+    written = part_m > float("-inf")
+    lse = torch.where(written, part_m + torch.log2(part_l), torch.full_like(part_m, float("-inf")))
+    o = torch.where(written[..., None], part_acc.float() / part_l[..., None], torch.zeros((), device=part_m.device))
+    return merge_partials(lse, o.contiguous(), out_dtype, return_lse=return_lse)
+
+
+def moba_forward(q, k, v, cfg: MoBAConfig, index: Optional[CSCIndex] = None, causal: bool = True,
+                 partials_dtype: Optional[torch.dtype] = None, cu_seqlens=None, max_seqlen=None):
+    """MoBA attention output [B,S,H,D] in the dtype of q (inference path; no
+    log-sum-exp kept). Reference: moba_fwd.py:783-835."""
+    if index is not None:
+        cu_seqlens, max_seqlen = index.cu_seqlens, index.max_seqlen
+    _validate(q, k, v, cfg, cu_seqlens, max_seqlen)
+    _lib.require_cuda(q, k, v, cu_seqlens)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    if index is None:
+        index = build_csc_fused(q, k, cfg, cu_seqlens=cu_seqlens, max_seqlen=max_seqlen)
+    part_lse, part_o = attend_partials(q, k, v, cfg, index, causal=causal, partials_dtype=partials_dtype)
+    return merge_partials(part_lse, part_o, q.dtype)

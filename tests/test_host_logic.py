@@ -1,0 +1,118 @@
+"""Host-side checks that need no GPU: configuration, validators, the C ABI."""
+
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+import moba_triton_b200 as moba
+from moba_triton_b200 import _lib
+from moba_triton_b200.kernels.moba_fwd import _validate
+from moba_triton_b200.varlen import from_nested, pack, unpack, validate_cu_seqlens
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_config_defaults_and_budget():
+    cfg = moba.MoBAConfig(block_size=128, top_k=8)
+    assert cfg.dtype is torch.bfloat16 and cfg.always_select_current and cfg.top_k_includes_current
+    assert cfg.past_blocks_selected(1024) == 7 and cfg.past_blocks_selected(3) == 3
+    assert cfg.num_blocks(200) == 2 and cfg.slots_per_query == 8
+    assert moba.MoBAConfig(32, 2, top_k_includes_current=False).slots_per_query == 3
+    assert moba.MoBAConfig(32, 2, always_select_current=False).slots_per_query == 2
+    with pytest.raises(ValueError):
+        moba.MoBAConfig(block_size=0, top_k=1)
+    with pytest.raises(Exception):
+        cfg.top_k = 3                                   # frozen
+
+
+def test_validate_messages_match_the_reference_keys():
+    cfg = moba.MoBAConfig(32, 4)
+    q = torch.zeros(1, 64, 4, 64)
+    with pytest.raises(ValueError, match="key/value"):
+        _validate(q, q, torch.zeros(1, 64, 2, 64), cfg)
+    with pytest.raises(ValueError, match="shape mismatch"):
+        _validate(q, torch.zeros(1, 32, 4, 64), torch.zeros(1, 32, 4, 64), cfg)
+    with pytest.raises(ValueError, match="divisible"):
+        _validate(q, torch.zeros(1, 64, 3, 64), torch.zeros(1, 64, 3, 64), cfg)
+    cu = torch.tensor([0, 64], dtype=torch.int32)
+    with pytest.raises(ValueError, match="batch 1"):
+        _validate(torch.zeros(2, 64, 4, 64), torch.zeros(2, 64, 4, 64), torch.zeros(2, 64, 4, 64), cfg, cu, 64)
+    with pytest.raises(ValueError, match="max_seqlen"):
+        _validate(q, q, q, cfg, cu, None)
+    with pytest.raises(ValueError, match="below the tl.dot minimum"):
+        _validate(q, q, q, moba.MoBAConfig(8, 2))
+    with pytest.raises(ValueError, match="power of two"):
+        _validate(torch.zeros(1, 64, 4, 48), torch.zeros(1, 64, 4, 48), torch.zeros(1, 64, 4, 48), cfg)
+    with pytest.raises(ValueError, match="cache line"):
+        _validate(torch.zeros(1, 64, 4, 16), torch.zeros(1, 64, 4, 16), torch.zeros(1, 64, 4, 16), cfg)
+
+
+def test_cu_seqlens_validation():
+    ok = torch.tensor([0, 80, 128], dtype=torch.int32)
+    assert validate_cu_seqlens(ok, 128, 80) == 2
+    for bad, msg in [(torch.tensor([[0, 1]], dtype=torch.int32), "1-D"),
+                     (torch.tensor([0], dtype=torch.int32), "two entries"),
+                     (torch.tensor([0, 128]), "int32"),
+                     (torch.tensor([1, 128], dtype=torch.int32), "start at 0"),
+                     (torch.tensor([0, 64, 64, 128], dtype=torch.int32), "strictly increasing"),
+                     (torch.tensor([0, 100], dtype=torch.int32), "total token count")]:
+        with pytest.raises(ValueError, match=msg):
+            validate_cu_seqlens(bad, 128, 128)
+    with pytest.raises(ValueError, match="below the longest"):
+        validate_cu_seqlens(ok, 128, 64)
+
+
+def test_pack_unpack_round_trip_and_nested():
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(3, 10, 2, 4, generator=g)
+    lens = [10, 3, 7]
+    mask = torch.arange(10)[None, :] < torch.tensor(lens)[:, None]
+    packed, cu, longest = pack(x, mask)
+    assert packed.shape == (1, 20, 2, 4) and cu.tolist() == [0, 10, 13, 20] and longest == 10
+    back = unpack(packed, cu, 3, 10)
+    assert torch.equal(back, x * mask[:, :, None, None])
+    nt = torch.nested.nested_tensor([x[i, :n] for i, n in enumerate(lens)], layout=torch.jagged)
+    p2, cu2, l2 = from_nested(nt)
+    assert torch.equal(p2, packed) and cu2.tolist() == cu.tolist() and l2 == 10
+
+
+def test_product_refuses_cpu_tensors_instead_of_falling_back():
+    cfg = moba.MoBAConfig(32, 4)
+    q = torch.zeros(1, 64, 2, 64)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        moba.moba_forward(q, q, q, cfg)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        moba.moba_attention(q, q, q, cfg)
+
+
+def test_library_loads_and_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "moba_b200.h")).read()
+    declared = set(re.findall(r"\b(moba_b200_[a-z_0-9]+)\s*\(", header))
+    assert declared == set(_lib.EXPORTS)
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert _lib.load().moba_b200_abi_version() == _lib.ABI_VERSION
+
+
+def test_c_abi_rejects_bad_problems_without_touching_a_gpu():
+    lib = _lib.load()
+    cfg = moba.MoBAConfig(32, 4)
+    prob = _lib.make_problem((1, 64, 3, 64), 2, torch.bfloat16, cfg)
+    assert lib.moba_b200_path_for(prob, _lib.STAGE_FWD) == -1
+    assert b"divisible" in lib.moba_b200_last_error()
+    prob = _lib.make_problem((1, 64, 2, 64), 2, torch.bfloat16, cfg)
+    assert lib.moba_b200_pool(prob, None, None, None, None) == -1
+    assert b"NULL" in lib.moba_b200_last_error()
+    assert lib.moba_b200_transpose_scratch_bytes(prob) == 1 * 2 * 2 * 1 * 1 * 4
+
+
+def test_product_never_imports_the_oracle():
+    pkg = os.path.join(ROOT, "moba_triton_b200")
+    for base, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh")):
+                assert "oracle" not in open(os.path.join(base, f)).read().replace("the oracle uses", ""), f
