@@ -103,6 +103,13 @@ long long moba_b200_launch_count(void);
 int moba_b200_profile_enable(int on);
 int moba_b200_profile_read(char* buf, size_t cap);
 
+/* Waits for `stream`, then copies the device's error word to *word and clears
+ * it. 0 means no kernel reported a problem; bit 0 = a bounded wait inside a
+ * tensor-core kernel gave up (its results are then invalid). Kernels never
+ * trap or spin forever; this is how such a failure is reported. No
+ * counterpart in the reference. */
+int moba_b200_device_status(unsigned int* word, void* stream);
+
 /* Which kernel family (MOBA_B200_PATH_PORTABLE or _TCGEN05) a stage would run
  * for this problem, or a negative error code. */
 int moba_b200_path_for(const moba_b200_problem* p, int stage);

@@ -25,6 +25,7 @@ EXPORTS = (
     "moba_b200_transpose_scratch_bytes", "moba_b200_pool", "moba_b200_gate",
     "moba_b200_transpose", "moba_b200_fwd", "moba_b200_merge", "moba_b200_bwd",
     "moba_b200_launch_count", "moba_b200_profile_enable", "moba_b200_profile_read",
+    "moba_b200_device_status",
 )
 
 
@@ -66,6 +67,7 @@ def load():
     lib.moba_b200_fwd.argtypes = [P, vp, vp, vp, I, vp, vp, vp, vp]
     lib.moba_b200_merge.argtypes = [P, vp, vp, vp, vp, vp]
     lib.moba_b200_bwd.argtypes = [P, vp, vp, vp, vp, vp, vp, vp, I, vp, vp, vp, vp, vp, vp, vp]
+    lib.moba_b200_device_status.argtypes = [POINTER(ctypes.c_uint), vp]
     lib.moba_b200_launch_count.restype = ctypes.c_longlong
     lib.moba_b200_profile_enable.argtypes = [c_int]
     lib.moba_b200_profile_read.argtypes = [ctypes.c_char_p, c_size_t]
@@ -84,6 +86,14 @@ def check(rc: int, what: str) -> None:
     if rc in (-1, -2):
         raise ValueError(f"{what}: {msg}")
     raise RuntimeError(f"{what}: {msg}")
+
+
+def device_status(device=None) -> int:
+    """Synchronises the current stream and returns (and clears) the device error
+    word: 0 when every tensor-core kernel ran to completion."""
+    word = ctypes.c_uint(0)
+    check(load().moba_b200_device_status(ctypes.byref(word), stream_ptr(device)), "device_status")
+    return int(word.value)
 
 
 def launch_count() -> int:

@@ -2,6 +2,7 @@
 // selection and the per-thread error text. Declarations and the reference
 // functions each entry point stands in for are in include/moba_b200.h.
 #include "common.cuh"
+#include "sm100.cuh"
 
 #include <stdarg.h>
 #include <string.h>
@@ -142,6 +143,19 @@ int moba_b200_profile_read(char* buf, size_t cap) {
   memcpy(buf, out.data(), n);
   buf[n] = 0;
   return (int)n;
+}
+
+int moba_b200_device_status(unsigned int* word, void* stream) {
+  // Waits for the stream, then reads and clears the current device's error word.
+  if (word == nullptr) { set_error("word is NULL"); return MOBA_B200_EINVAL; }
+  unsigned* dev_word = device_error_word();
+  if (dev_word == nullptr) { set_error("no device error word (no CUDA device?)"); return MOBA_B200_ECUDA; }
+  cudaStream_t st = (cudaStream_t)stream;
+  MOBA_CUDA_OK(cudaMemcpyAsync(word, dev_word, sizeof(unsigned), cudaMemcpyDeviceToHost, st));
+  MOBA_CUDA_OK(cudaMemsetAsync(dev_word, 0, sizeof(unsigned), st));
+  MOBA_CUDA_OK(cudaStreamSynchronize(st));
+  if (*word) set_error("device error word 0x%x (1 = a bounded wait inside a kernel gave up)", *word);
+  return MOBA_B200_OK;
 }
 
 int moba_b200_path_for(const moba_b200_problem* p, int stage) {

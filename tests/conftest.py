@@ -93,3 +93,12 @@ def make_qkv(shape, hkv=None, dtype=torch.float32, seed=0, with_do=False):
     if with_do:
         out.append((torch.randn(shape, generator=g) * 0.1).to(torch.bfloat16).to(dtype))
     return tuple(out)
+
+
+@pytest.fixture(autouse=True)
+def _device_error_word_stays_clear(request):
+    """After every GPU test: no kernel may have reported a bounded wait giving up."""
+    yield
+    if request.node.get_closest_marker("gpu") is not None and torch.cuda.is_available():
+        from moba_triton_b200 import _lib
+        assert _lib.device_status() == 0, "a tensor-core kernel reported an error"
