@@ -322,6 +322,14 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       if (!load_column(c, item, ix, p, cu, n_kv_rows)) continue;
       const int nt = (c.n + kTile - 1) / kTile;
       if (c.keys < kTile) {
+        // Publish the previous column's last tile first: the K load awaited below is
+        // issued only after that tile's MMA has run.
+        if (pending >= 0) {
+          cp_async_wait<0>();
+          fence_proxy_async();
+          mbar_arrive(&bars->q_full[pending]);
+          pending = -1;
+        }
         // zero the rows of K and V past the end of the sequence (they belong to the next one)
         const int dead = kTile - c.keys;
         mbar_wait(&bars->k_full, it_cnt & 1, wc);

@@ -2,7 +2,5 @@
 #include "common.cuh"
 namespace moba {
 bool gate_sm100_supported(const moba_b200_problem&) { return false; }
-bool bwd_sm100_supported(const moba_b200_problem&) { return false; }
 int launch_gate_sm100(const moba_b200_problem&, const void*, const void*, const int32_t*, int32_t*, cudaStream_t) { return MOBA_B200_EUNSUPPORTED; }
-int launch_bwd_sm100(const moba_b200_problem&, const void*, const void*, const void*, const void*, const float*, const float*, const moba_b200_index&, const int32_t*, void*, void*, void*, cudaStream_t) { return MOBA_B200_EUNSUPPORTED; }
 }
