@@ -55,6 +55,21 @@ int encode_2d_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t di
   return MOBA_B200_OK;
 }
 
+// Block means [kv_rows][blocks][dim]: box of (64, 128 blocks, 1 row).
+int encode_kbar_map_impl(CUtensorMap* out, const void* base, uint64_t kv_rows, uint64_t nb, uint64_t dim) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return MOBA_B200_ECUDA; }
+  const cuuint64_t dims[3] = {dim, nb, kv_rows};
+  const cuuint64_t strides[2] = {dim * 2, nb * dim * 2};
+  const cuuint32_t box[3] = {64, 128, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with code %d", (int)r); return MOBA_B200_ECUDA; }
+  return MOBA_B200_OK;
+}
+
 // one word per device of this process, zero-initialised with the module
 __device__ unsigned g_error_word;
 
