@@ -7,10 +7,14 @@
 //   loader (1 thread)  TMA: the Q tile once, then block-mean chunks of 128 blocks
 //   mma    (1 thread)  S = Q Kbar^T (M128 N128 K=D) into one of two TMEM buffers
 //   select (2 x 4 warps, alternating chunks) tcgen05.ld one row per thread,
-//          round to the input dtype, compare with the row's entry bar; the rare
-//          winner enters a per-thread list (ties: admission needs strictly
-//          greater, eviction drops the highest id among the weakest)
-// At the end each thread emits its list plus the own block, ascending, -1 padded.
+//          round each score to the input dtype and pack it with its block id
+//          into one sortable 32-bit key (score bits made monotone in the high
+//          half, 0xFFFF - id in the low half), so "score descending, ties to
+//          the lower id" is plain integer order. Each thread keeps its best
+//          keys in a sorted register list; groups of four keys are skipped
+//          with one compare when none can enter.
+// At the end the two warpgroups' lists are merged and each thread emits its
+// ids plus the own block, ascending, -1 padded.
 //
 // Scores are float32 tensor-core sums rounded to the input dtype; the portable
 // gate rounds the exact sum. The two differ only when a float32 partial sum
@@ -46,20 +50,35 @@ struct Bars {
   int abort;
 };
 
-// Offers (s, blk) to the list; returns the new entry bar (the weakest kept score,
-// -inf while a slot is empty). Kept out of line: it runs a few dozen times per row.
-__device__ __noinline__ float list_insert(float* vals, int* ids, int take, float s, int blk) {
-  int w = 0;
-  for (int e = 1; e < take; ++e)
-    if (vals[e] < vals[w] || (vals[e] == vals[w] && ids[e] > ids[w])) w = e;
-  vals[w] = s;
-  ids[w] = blk;
-  float m = vals[0];
-  for (int e = 1; e < take; ++e) m = fminf(m, vals[e]);
-  return m;
+// Sorted (descending) register list of the L best keys seen so far.
+template <int L>
+__device__ __forceinline__ void list_offer(uint32_t (&t)[L], uint32_t x) {
+#pragma unroll
+  for (int i = 0; i < L; ++i) {
+    const uint32_t hi = max(t[i], x);
+    x = min(t[i], x);
+    t[i] = hi;
+  }
 }
 
-template <int D, typename T>
+// Two 16-bit floats (packed) -> two 16-bit keys whose unsigned order is the
+// numeric order: negative values have all bits flipped, the others only the sign.
+__device__ __forceinline__ uint32_t monotone16x2(uint32_t w) {
+  const uint32_t neg = ((w >> 15) & 0x00010001u) * 0x7FFFu;
+  return w ^ (neg | 0x80008000u);
+}
+
+template <typename T> __device__ __forceinline__ uint32_t round_pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t round_pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t round_pack2<__half>(float a, float b) {
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int D, typename T, int L>
 __global__ void __launch_bounds__(kThreads, 2)
 gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kb_map,
                   const int32_t* __restrict__ cu, int32_t* __restrict__ block_idx, moba_b200_problem p,
@@ -105,11 +124,9 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     const int wg = warp >> 2;
     const int r = (warp & 3) * 32 + lane;
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
-    float vals[kMaxTake];
-    int ids[kMaxTake];
+    uint32_t best[L];
 #pragma unroll
-    for (int e = 0; e < kMaxTake; ++e) { vals[e] = -INFINITY; ids[e] = kEmpty; }
-    float thr = -INFINITY;
+    for (int e = 0; e < L; ++e) best[e] = 0u;                   // 0 sorts below every real key
     // The two warpgroups take alternate chunks of the same 128 rows, so each keeps
     // its own list per row; the lists are merged at the end through shared memory.
     for (int c = wg; c < n_chunks; c += 2) {
@@ -118,64 +135,70 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
       tc_fence_after();
       const int c0 = c * kTile;
       const int cmax = tile - c0;                               // columns [0, cmax) are candidates
+      const bool full = cmax >= kTile;
       uint32_t v[32];
 #pragma unroll 1
       for (int ch = 0; ch < 4; ++ch) {
         tmem_ld32(tmem + lane_off + wg * 128 + ch * 32, v);
         tmem_ld_wait();
+        const uint32_t inv0 = 0xFFFFu - (uint32_t)(c0 + ch * 32);   // low half of column 0's key
 #pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          const int col = ch * 32 + k;
-          const float s = Elem<T>::round_f(__uint_as_float(v[k]));
-          if (col < cmax && s > thr) thr = list_insert(vals, ids, take, s, c0 + col);
+        for (int g = 0; g < 8; ++g) {
+          const uint32_t w0 = monotone16x2(round_pack2<T>(__uint_as_float(v[g * 4 + 0]), __uint_as_float(v[g * 4 + 1])));
+          const uint32_t w1 = monotone16x2(round_pack2<T>(__uint_as_float(v[g * 4 + 2]), __uint_as_float(v[g * 4 + 3])));
+          uint32_t k0 = (w0 << 16) | (inv0 - (g * 4 + 0));
+          uint32_t k1 = (w0 & 0xFFFF0000u) | (inv0 - (g * 4 + 1));
+          uint32_t k2 = (w1 << 16) | (inv0 - (g * 4 + 2));
+          uint32_t k3 = (w1 & 0xFFFF0000u) | (inv0 - (g * 4 + 3));
+          if (!full) {
+            const int col = ch * 32 + g * 4;
+            k0 = (col + 0 < cmax) ? k0 : 0u;
+            k1 = (col + 1 < cmax) ? k1 : 0u;
+            k2 = (col + 2 < cmax) ? k2 : 0u;
+            k3 = (col + 3 < cmax) ? k3 : 0u;
+          }
+          if (max(max(k0, k1), max(k2, k3)) > best[L - 1]) {
+            list_offer<L>(best, k0);
+            list_offer<L>(best, k1);
+            list_offer<L>(best, k2);
+            list_offer<L>(best, k3);
+          }
         }
       }
       tc_fence_before();
       mbar_arrive(&bars->s_free[wg]);
     }
     // ---- merge the two warpgroups' lists (warpgroup 1 -> shared -> warpgroup 0) ----
-    float* xv = reinterpret_cast<float*>(sKb);                  // Kbar stages are idle now
-    int* xi = reinterpret_cast<int*>(sKb + kTile * kMaxTake * 4);
+    uint32_t* xk = reinterpret_cast<uint32_t*>(sKb);            // the Kbar stages are idle by now
     asm volatile("bar.sync 2, 256;" ::: "memory");              // every S MMA has been consumed
     if (wg == 1) {
-      for (int e = 0; e < take; ++e) { xv[r * kMaxTake + e] = vals[e]; xi[r * kMaxTake + e] = ids[e]; }
+#pragma unroll
+      for (int e = 0; e < L; ++e) xk[e * kTile + r] = best[e];
     }
     asm volatile("bar.sync 2, 256;" ::: "memory");
     if (wg == 0 && row0 + r < sp.len) {
-      // The final selection is the best `take` of the union of both lists. Rebuild
-      // it by offering the union in ascending block order, so the admission rule
-      // (strictly greater: the earlier block wins a tie) applies unchanged.
-      float av[2 * kMaxTake];
-      int ai[2 * kMaxTake];
-      int n = 0;
-      for (int e = 0; e < take; ++e) if (ids[e] != kEmpty) { av[n] = vals[e]; ai[n] = ids[e]; ++n; }
-      for (int e = 0; e < take; ++e) {
-        const int id = xi[r * kMaxTake + e];
-        if (id != kEmpty) { av[n] = xv[r * kMaxTake + e]; ai[n] = id; ++n; }
+#pragma unroll
+      for (int e = 0; e < L; ++e) list_offer<L>(best, xk[e * kTile + r]);
+      // ---- emit: the best `take` ids plus the own block, ascending, -1 padded ----
+      int ids[L];
+      int kept = 0;
+#pragma unroll
+      for (int e = 0; e < L; ++e) {
+        const bool ok = e < take && best[e] != 0u;
+        ids[e] = ok ? (int)(0xFFFFu - (best[e] & 0xFFFFu)) : kEmpty;
+        kept += ok ? 1 : 0;
       }
-      for (int i = 1; i < n; ++i) {                             // insertion sort by id
-        const float tv = av[i]; const int ti = ai[i];
-        int j = i - 1;
-        while (j >= 0 && ai[j] > ti) { av[j + 1] = av[j]; ai[j + 1] = ai[j]; --j; }
-        av[j + 1] = tv; ai[j + 1] = ti;
-      }
-      for (int e = 0; e < take; ++e) { vals[e] = -INFINITY; ids[e] = kEmpty; }
-      thr = -INFINITY;
-      for (int i = 0; i < n; ++i)
-        if (av[i] > thr) thr = list_insert(vals, ids, take, av[i], ai[i]);
-      // ---- emit: kept ids plus the own block, ascending, -1 padded ----
-      int out[kMaxTake + 1];
-      int m = 0;
-      for (int e = 0; e < take; ++e) if (ids[e] != kEmpty) out[m++] = ids[e];
-      for (int i = 1; i < m; ++i) {
-        const int ti = out[i];
-        int j = i - 1;
-        while (j >= 0 && out[j] > ti) { out[j + 1] = out[j]; --j; }
-        out[j + 1] = ti;
-      }
-      if (p.always_current) out[m++] = tile;                    // larger than every candidate
       int32_t* dst = block_idx + ((b * p.q_heads + hq) * p.tokens + sp.bos + row0 + r) * (size_t)p.slots;
-      for (int e = 0; e < p.slots; ++e) dst[e] = (e < m) ? out[e] : -1;
+#pragma unroll
+      for (int e = 0; e < L; ++e) {                             // rank by id: position in the output
+        if (ids[e] == kEmpty) continue;
+        int rank = 0;
+#pragma unroll
+        for (int f = 0; f < L; ++f) rank += (ids[f] < ids[e]) ? 1 : 0;
+        dst[rank] = ids[e];
+      }
+      if (p.always_current) dst[kept++] = tile;                 // the own block is past every candidate
+      for (int e = kept; e < p.slots; ++e) dst[e] = -1;
     }
   } else if (warp == kMmaWarp) {
     if (lane == 0 && n_chunks > 0) {
@@ -221,10 +244,10 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
 }
 
 
-template <int D, typename T>
+template <int D, typename T, int L>
 int launch_one(const moba_b200_problem& p, const CUtensorMap& qm, const CUtensorMap& km, const int32_t* cu,
                int32_t* block_idx, unsigned* err, cudaStream_t st) {
-  auto kern = gate_sm100_kernel<D, T>;
+  auto kern = gate_sm100_kernel<D, T, L>;
   MOBA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GateCfg<D>::kSmem));
   const int n_tiles = (p.max_seqlen + kTile - 1) / kTile;
   dim3 grid(n_tiles, p.n_seq * p.q_heads);
@@ -238,6 +261,7 @@ int launch_one(const moba_b200_problem& p, const CUtensorMap& qm, const CUtensor
 bool gate_sm100_supported(const moba_b200_problem& p) {
   return (p.dtype == MOBA_B200_BF16 || p.dtype == MOBA_B200_F16) && p.block_size == 128 &&
          (p.head_dim == 64 || p.head_dim == 128) && p.take <= kMaxTake && p.slots <= kMaxTake + 1 &&
+         p.num_blocks <= 0xFFFF &&
          (long long)p.batch * p.tokens < 0x7fffffffLL;
 }
 
@@ -254,12 +278,11 @@ int launch_gate_sm100(const moba_b200_problem& p, const void* q, const void* kba
   rc = encode_kbar_map_impl(&km, kbar, (uint64_t)p.n_seq * p.kv_heads, p.num_blocks, p.head_dim);
   if (rc) return rc;
   const bool bf = p.dtype == MOBA_B200_BF16;
-  if (p.head_dim == 64) {
-    if (bf) return launch_one<64, __nv_bfloat16>(p, qm, km, cu, block_idx, err, st);
-    return launch_one<64, __half>(p, qm, km, cu, block_idx, err, st);
-  }
-  if (bf) return launch_one<128, __nv_bfloat16>(p, qm, km, cu, block_idx, err, st);
-  return launch_one<128, __half>(p, qm, km, cu, block_idx, err, st);
+#define GO(D, T) return (p.take <= 7) ? launch_one<D, T, 7>(p, qm, km, cu, block_idx, err, st) \
+                                      : launch_one<D, T, 8>(p, qm, km, cu, block_idx, err, st)
+  if (p.head_dim == 64) { if (bf) GO(64, __nv_bfloat16); else GO(64, __half); }
+  if (bf) GO(128, __nv_bfloat16); else GO(128, __half);
+#undef GO
 }
 
 }  // namespace moba
