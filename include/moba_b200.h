@@ -138,6 +138,25 @@ int moba_b200_transpose(const moba_b200_problem* p, const int32_t* block_idx,
                         int32_t* slot_of_pair, void* scratch, size_t scratch_bytes,
                         void* stream);
 
+/* moba_b200_transpose for callers that cannot allocate device memory -- a
+ * server that fixes its whole memory plan at start-up and forbids cudaMalloc
+ * later, or a plugin that receives only its input and output buffers. The
+ * scratch is an 8 MiB array built into the library (each GPU that loads the
+ * library holds it until the process exits); problems whose
+ * moba_b200_transpose_scratch_bytes() exceeds 8 MiB are refused with
+ * MOBA_B200_EUNSUPPORTED. Inputs and outputs are the caller's, exactly as for
+ * moba_b200_transpose, and the results are identical. The call allocates and
+ * frees nothing. The first call on a device looks up the array's device
+ * address (with that device current); make that first call before starting
+ * any stream capture. All calls share the one array and nothing in it needs
+ * clearing between calls, but two calls that overlap on the same GPU (two
+ * streams, two threads) race on it: serialise them.
+ * This entry point has no counterpart in the reference. */
+int moba_b200_transpose_noalloc(const moba_b200_problem* p, const int32_t* block_idx,
+                                const int32_t* cu_seqlens, int32_t* col_nnz, int32_t* col_offsets,
+                                int32_t* order, int32_t* row_indices, int32_t* head_indices,
+                                int32_t* slot_of_pair, void* stream);
+
 /* KV-block-major attention: one K/V block resident per CTA, the queries that
  * selected it gathered through the index; writes normalised partial outputs and
  * their log2-sum-exp per (query, slot). Resets part_lse to -inf first.

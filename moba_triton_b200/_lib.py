@@ -25,7 +25,7 @@ EXPORTS = (
     "moba_b200_transpose_scratch_bytes", "moba_b200_pool", "moba_b200_gate",
     "moba_b200_transpose", "moba_b200_fwd", "moba_b200_merge", "moba_b200_bwd",
     "moba_b200_launch_count", "moba_b200_profile_enable", "moba_b200_profile_read",
-    "moba_b200_device_status",
+    "moba_b200_device_status", "moba_b200_transpose_noalloc",
 )
 
 
@@ -64,6 +64,7 @@ def load():
     lib.moba_b200_pool.argtypes = [P, vp, vp, vp, vp]
     lib.moba_b200_gate.argtypes = [P, vp, vp, vp, vp, vp]
     lib.moba_b200_transpose.argtypes = [P, vp, vp, vp, vp, vp, vp, vp, vp, vp, c_size_t, vp]
+    lib.moba_b200_transpose_noalloc.argtypes = [P, vp, vp, vp, vp, vp, vp, vp, vp, vp]
     lib.moba_b200_fwd.argtypes = [P, vp, vp, vp, I, vp, vp, vp, vp]
     lib.moba_b200_merge.argtypes = [P, vp, vp, vp, vp, vp]
     lib.moba_b200_bwd.argtypes = [P, vp, vp, vp, vp, vp, vp, vp, I, vp, vp, vp, vp, vp, vp, vp]

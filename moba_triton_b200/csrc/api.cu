@@ -208,6 +208,20 @@ int moba_b200_transpose(const moba_b200_problem* p, const int32_t* block_idx,
                           head_indices, slot_of_pair, scratch, scratch_bytes, (cudaStream_t)stream);
 }
 
+int moba_b200_transpose_noalloc(const moba_b200_problem* p, const int32_t* block_idx,
+                                const int32_t* cu_seqlens, int32_t* col_nnz, int32_t* col_offsets,
+                                int32_t* order, int32_t* row_indices, int32_t* head_indices,
+                                int32_t* slot_of_pair, void* stream) {
+  MOBA_TRY(check_problem(p));
+  MOBA_TRY(need(block_idx, "block_idx")); MOBA_TRY(need(col_nnz, "col_nnz"));
+  MOBA_TRY(need(col_offsets, "col_offsets")); MOBA_TRY(need(order, "order"));
+  MOBA_TRY(need(row_indices, "row_indices")); MOBA_TRY(need(head_indices, "head_indices"));
+  MOBA_TRY(need(slot_of_pair, "slot_of_pair"));
+  if (p->packed) MOBA_TRY(need(cu_seqlens, "cu_seqlens"));
+  return launch_transpose_noalloc(*p, block_idx, cu_seqlens, col_nnz, col_offsets, order, row_indices,
+                                  head_indices, slot_of_pair, (cudaStream_t)stream);
+}
+
 static int check_index(const moba_b200_problem* p, const moba_b200_index* ix) {
   MOBA_TRY(need(ix, "index"));
   MOBA_TRY(need(ix->col_nnz, "index.col_nnz")); MOBA_TRY(need(ix->col_offsets, "index.col_offsets"));

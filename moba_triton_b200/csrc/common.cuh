@@ -105,6 +105,10 @@ int launch_transpose(const moba_b200_problem& p, const int32_t* block_idx, const
                      int32_t* heads, int32_t* slots, void* scratch, size_t scratch_bytes,
                      cudaStream_t st);
 
+int launch_transpose_noalloc(const moba_b200_problem& p, const int32_t* block_idx, const int32_t* cu,
+                             int32_t* col_nnz, int32_t* col_offsets, int32_t* order, int32_t* rows,
+                             int32_t* heads, int32_t* slots, cudaStream_t st);
+
 int launch_fill_lse(const moba_b200_problem& p, float* part_lse, cudaStream_t st);
 int launch_fwd_portable(const moba_b200_problem& p, const void* q, const void* k, const void* v,
                         const moba_b200_index& ix, const int32_t* cu, void* part_o,

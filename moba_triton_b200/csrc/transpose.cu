@@ -19,6 +19,8 @@
 // inside a column to the scheduler.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace moba {
 
 struct TransposeGeom {
@@ -256,6 +258,60 @@ int launch_transpose(const moba_b200_problem& p, const int32_t* block_idx, const
                                                      slots, p, g.chunk_rows, g.chunks, capacity);
   MOBA_LAUNCH_OK("scatter_kernel"); }
   return MOBA_B200_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Transpose for callers that cannot hand over scratch memory.
+//
+// Some hosts of this library may not allocate device memory at all: a serving
+// process that lays out every byte of the GPU at start-up and forbids cudaMalloc
+// afterwards (it synchronises the device and can fail once memory is
+// fragmented), or a plugin that is handed nothing but its input and output
+// buffers and has no allocator to ask. For them the per-chunk histogram of the
+// transpose lives in this fixed array inside the library image. Every GPU that
+// loads the library keeps these 8 MiB until the process exits.
+//
+// `g_transpose_scratch` names the array in device code. In host code the same
+// name is only a handle for cudaGetSymbolAddress: passing it to a kernel as a
+// pointer would hand the kernel a host address.
+// ---------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = size_t(8) << 20;
+static __device__ __align__(256) unsigned char g_transpose_scratch[kStaticScratchBytes];
+
+// Device address of the array on the current device; looked up once per device,
+// with that device current, and cached.
+static int static_scratch_address(void** out) {
+  static void* table[64] = {nullptr};
+  static std::mutex mu;
+  int dev = -1;
+  MOBA_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) { set_error("device ordinal %d out of range", dev); return MOBA_B200_EUNSUPPORTED; }
+  std::lock_guard<std::mutex> lock(mu);
+  if (table[dev] == nullptr) {
+    void* ptr = nullptr;
+    MOBA_CUDA_OK(cudaGetSymbolAddress(&ptr, g_transpose_scratch));
+    table[dev] = ptr;
+  }
+  *out = table[dev];
+  return MOBA_B200_OK;
+}
+
+int launch_transpose_noalloc(const moba_b200_problem& p, const int32_t* block_idx, const int32_t* cu,
+                             int32_t* col_nnz, int32_t* col_offsets, int32_t* order, int32_t* rows,
+                             int32_t* heads, int32_t* slots, cudaStream_t st) {
+  const size_t need = transpose_scratch_bytes(p);
+  if (need > kStaticScratchBytes) {
+    set_error("transpose without caller scratch: this problem needs %zu bytes of scratch, the built-in "
+              "array holds %zu; use moba_b200_transpose with a caller buffer", need, kStaticScratchBytes);
+    return MOBA_B200_EUNSUPPORTED;
+  }
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != MOBA_B200_OK) return rc;
+  // Nothing in the array has to start at zero: the count pass writes every entry the
+  // scan pass reads, so the previous call's contents are simply overwritten.
+  return launch_transpose(p, block_idx, cu, col_nnz, col_offsets, order, rows, heads, slots, scratch,
+                          kStaticScratchBytes, st);
 }
 
 }  // namespace moba
