@@ -319,13 +319,20 @@ def run_ours(args, wl, rank, world, local_rank):
             ms = float(t)
         return ms
 
-    for _ in range(args.warmup):
-        step()
+    # nvidia-smi needs a few hundred ms to deliver its first sample, so the sampler runs from
+    # the warm-up on, and the same step keeps running (untimed) after the timed region until
+    # the sampler has had about a second under this load.
     clocks = ClockSampler(local_rank)
     clocks.start()
+    t_load = time.perf_counter()
+    for _ in range(args.warmup):
+        step()
     launches0 = _lib.launch_count()
     ms_total = timed(step, args.steps)
     launches = _lib.launch_count() - launches0
+    while time.perf_counter() - t_load < 1.2:
+        step()
+    torch.cuda.synchronize()
     clock_info = clocks.stop()
     ms_step = ms_total / args.steps
 

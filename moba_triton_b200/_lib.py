@@ -11,7 +11,7 @@ from ctypes import POINTER, Structure, c_char_p, c_int, c_int32, c_int64, c_size
 import torch
 
 PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG, "libmoba_b200.so")
+LIB_PATH = os.environ.get("MOBA_B200_LIBRARY", os.path.join(PKG, "libmoba_b200.so"))
 
 F32, BF16, F16 = 0, 1, 2
 PATH_AUTO, PATH_PORTABLE, PATH_TCGEN05 = 0, 1, 2

@@ -120,7 +120,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_kv_rows = p.n_seq * p.kv_heads;
+#ifdef MOBA_WAIT_STATS
+  const WaitCtx wc{&bars->abort, error_word, nullptr};
+#else
   const WaitCtx wc{&bars->abort, error_word};
+#endif
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
@@ -167,15 +171,28 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       const int32_t* rows_i = ix.row_indices + (size_t)c.kv_row * ix.capacity + c.lo;
       const int32_t* heads_i = ix.head_indices + (size_t)c.kv_row * ix.capacity + c.lo;
       const int32_t* slots_i = ix.slot_of_pair + (size_t)c.kv_row * ix.capacity + c.lo;
+      // Software pipeline over the column's tiles: the index entry is fetched two tiles
+      // ahead and the row's lse / delta one tile ahead, so neither load is waited for.
+      int row = 0, head = 0, slot = 0, row1 = 0, head1 = 0, slot1 = 0;
+      float lse_r = 0.f, delta_r = 0.f;
+      if (r < c.n) {
+        row = rows_i[r]; head = heads_i[r]; slot = slots_i[r];
+        const size_t qr = (c.b * p.q_heads + head) * p.tokens + row;
+        lse_r = lse[qr]; delta_r = delta[qr];
+      }
+      if (kTile + r < c.n) { row1 = rows_i[kTile + r]; head1 = heads_i[kTile + r]; slot1 = slots_i[kTile + r]; }
       for (int i = 0; i < nt; ++i, ++t) {
         const int e = i * kTile + r;
         const bool live = e < c.n;
-        const int row = live ? rows_i[e] : 0;
-        const int head = live ? heads_i[e] : 0;
-        const int slot = live ? slots_i[e] : 0;
         const size_t qrow = (c.b * p.q_heads + head) * p.tokens + row;
-        const float lse_r = live ? lse[qrow] : 0.f;
-        const float delta_r = live ? delta[qrow] : 0.f;
+        // issue the loads of the following tiles now; they are consumed at the bottom
+        float lse_n = 0.f, delta_n = 0.f;
+        int row2 = 0, head2 = 0, slot2 = 0;
+        if (e + kTile < c.n) {
+          const size_t qn = (c.b * p.q_heads + head1) * p.tokens + row1;
+          lse_n = lse[qn]; delta_n = delta[qn];
+        }
+        if (e + 2 * kTile < c.n) { row2 = rows_i[e + 2 * kTile]; head2 = heads_i[e + 2 * kTile]; slot2 = slots_i[e + 2 * kTile]; }
         int jmax = live ? c.keys - 1 : -1;             // dead rows contribute nothing
         if (p.causal && live && (row - c.bos) / kTile == c.blk) jmax = min(jmax, row - c.key0);
 
@@ -227,6 +244,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         }
         tc_fence_before();
         mbar_arrive(&bars->dq_read);
+        row = row1; head = head1; slot = slot1; lse_r = lse_n; delta_r = delta_n;
+        row1 = row2; head1 = head2; slot1 = slot2;
       }
       // ---- the column's dV (warpgroup 0) and dK (warpgroup 1), one key row per thread ----
       mbar_wait(&bars->acc_full, it_cnt & 1, wc);
@@ -371,11 +390,14 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       }
       const int32_t* rows_i = ix.row_indices + (size_t)c.kv_row * ix.capacity + c.lo;
       const int32_t* heads_i = ix.head_indices + (size_t)c.kv_row * ix.capacity + c.lo;
+      int n_row = 0, n_head = 0;                           // index entry of the next tile, fetched ahead
+      if (pt < c.n) { n_row = rows_i[pt]; n_head = heads_i[pt]; }
       for (int i = 0; i < nt; ++i, ++t) {
         const uint32_t st = t % NST, us = t / NST;
         const int e = i * kTile + pt;
         long long off = -1;
-        if (e < c.n) off = (long long)(((c.b * p.tokens + rows_i[e]) * p.q_heads + heads_i[e]) * (size_t)D);
+        if (e < c.n) off = (long long)(((c.b * p.tokens + n_row) * p.q_heads + n_head) * (size_t)D);
+        if (e + kTile < c.n) { n_row = rows_i[e + kTile]; n_head = heads_i[e + kTile]; }
         if (us >= 1) mbar_wait(&bars->qd_empty[st], (us - 1) & 1, wc);
         bars->row_off[pt] = off;
         asm volatile("bar.sync 1, 128;" ::: "memory");

@@ -101,7 +101,11 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
   const size_t b = p.packed ? 0 : (size_t)seq;
   const int take = p.take;
   const int n_chunks = (take > 0) ? (tile + kTile - 1) / kTile : 0;   // candidates: blocks [0, tile)
+#ifdef MOBA_WAIT_STATS
+  const WaitCtx wc{&bars->abort, error_word, nullptr};
+#else
   const WaitCtx wc{&bars->abort, error_word};
+#endif
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);

@@ -53,16 +53,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 struct WaitCtx {
   volatile int* abort;        // shared-memory flag of the CTA
   unsigned* error_word;       // global
+#ifdef MOBA_WAIT_STATS
+  unsigned long long* stats;  // shared-memory cycle counters, one per wait site (debug builds)
+#endif
 };
 
 constexpr uint32_t kWaitTries = 1u << 22;   // each try suspends for a while in hardware
 
 // Waits for the phase with the given parity to complete. Returns false (and
 // latches the abort flag) if it gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, int site = 0) {
   if (*ctx.abort) return false;
+#ifdef MOBA_WAIT_STATS
+  const long long t0__ = clock64();
+#endif
   for (uint32_t i = 0; i < kWaitTries; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) {
+#ifdef MOBA_WAIT_STATS
+      if (ctx.stats != nullptr) atomicAdd(&ctx.stats[site], (unsigned long long)(clock64() - t0__));
+#endif
+      return true;
+    }
     if ((i & 1023u) == 1023u && *ctx.abort) return false;
   }
   *ctx.abort = 1;
@@ -149,6 +160,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Same wait, but also names registers of the load it guards as in/out operands, so the compiler
+// cannot schedule their first use above the wait.
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[7]), "+r"(r[8]), "+r"(r[15]), "+r"(r[16]), "+r"(r[23]), "+r"(r[24]), "+r"(r[31])
+               :: "memory");
+}
 
 // ---------------------------------------------------------------------------
 // descriptors
