@@ -4,7 +4,7 @@
 // Persistent CTAs (one per SM) walk the (sequence, kv head, block) columns in
 // longest-first order, round-robin. Per column:
 //   loader   (1 thread)  TMA: the K block and the V block -> swizzled smem, once
-//   gather   (4 warps)   cp.async: 128 selected query rows per tile -> swizzled smem
+//   gather   (2 warps)   cp.async: 128 selected query rows per tile -> swizzled smem
 //   mma      (1 thread)  S = Q K^T (M128 N128 K=D) and O = P V (M128 N=D K128) into TMEM
 //   softmax  (2 x 4 warps, alternating tiles) tcgen05.ld S, mask, exp2, row sum,
 //            P (16-bit) -> smem; then tcgen05.ld O, normalise, store the partial
@@ -26,9 +26,9 @@ namespace {
 
 constexpr int kTile = 128;                 // queries per tile == keys per block
 constexpr int kSub = kTile * 128;          // bytes of one [128 rows][64 elems] swizzled sub-tile
-constexpr int kSoftmaxThreads = 256;
 constexpr int kMmaWarp = 8, kLoadWarp = 9, kGatherWarp0 = 10;
-constexpr int kThreads = 14 * 32;
+constexpr int kGatherThreads = 64;           // two gather warps, two rows of a tile per thread
+constexpr int kThreads = 12 * 32;            // 384 threads: up to 168 registers each
 
 template <int D> struct FwdCfg {
   static constexpr int kSubs = D / 64;                 // sub-tiles per operand along the head dim
@@ -36,7 +36,7 @@ template <int D> struct FwdCfg {
   static constexpr int kQStages = (D == 64) ? 3 : 2;
   static constexpr int kPBytes = 2 * kSub;             // [128][128] 16-bit
   static constexpr int kSmemData = 2 * kOperand + kQStages * kOperand + 2 * kPBytes;
-  static constexpr int kSmem = kSmemData + 1024 /*align*/ + 2048 /*barriers, pointers*/;
+  static constexpr int kSmem = kSmemData + 1024 /*align*/ + 6144 /*barriers, pointers*/;
 };
 
 struct Bars {
@@ -45,7 +45,11 @@ struct Bars {
   uint64_t s_full[2], p_full[2], o_full[2], so_free[2];
   uint32_t tmem_base;
   int abort;
-  const void* row_ptr[kTile];              // gather sources of the current tile (nullptr = dead row)
+#ifdef MOBA_WAIT_STATS
+  unsigned long long stats[16];            // debug builds: cycles per wait site / section
+#endif
+  unsigned char* out_ptr[2][kTile];        // destination rows of the tile each warpgroup is storing
+  const void* row_ptr[2][kTile];           // gather sources of two consecutive tiles (nullptr = dead row)
 };
 
 struct Column {                            // one unit of work
@@ -103,13 +107,23 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_kv_rows = p.n_seq * p.kv_heads;
+#ifdef MOBA_WAIT_STATS
+  const WaitCtx wc{&bars->abort, error_word, bars->stats};
+  if (threadIdx.x < 16) bars->stats[threadIdx.x] = 0;
+  const long long kernel_t0 = clock64();
+#define STAT_T0() long long st0__ = clock64()
+#define STAT_ADD(site) do { long long n__ = clock64(); atomicAdd(&bars->stats[site], (unsigned long long)(n__ - st0__)); st0__ = clock64(); } while (0)
+#else
   const WaitCtx wc{&bars->abort, error_word};
+#define STAT_T0() do {} while (0)
+#define STAT_ADD(site) do {} while (0)
+#endif
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->k_full, 1); mbar_init(&bars->v_full, 1);
-    mbar_init(&bars->k_fix, 128); mbar_init(&bars->v_fix, 128);
+    mbar_init(&bars->k_fix, kGatherThreads); mbar_init(&bars->v_fix, kGatherThreads);
     mbar_init(&bars->k_free, 1); mbar_init(&bars->v_free, 1);
-    for (int i = 0; i < 3; ++i) { mbar_init(&bars->q_full[i], 128); mbar_init(&bars->q_empty[i], 1); }
+    for (int i = 0; i < 3; ++i) { mbar_init(&bars->q_full[i], kGatherThreads); mbar_init(&bars->q_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->s_full[i], 1); mbar_init(&bars->p_full[i], 128);
       mbar_init(&bars->o_full[i], 1); mbar_init(&bars->so_free[i], 128);
@@ -141,95 +155,126 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       const int32_t* rows_i = ix.row_indices + (size_t)c.kv_row * ix.capacity + c.lo;
       const int32_t* heads_i = ix.head_indices + (size_t)c.kv_row * ix.capacity + c.lo;
       const int32_t* slots_i = ix.slot_of_pair + (size_t)c.kv_row * ix.capacity + c.lo;
-      for (int i = 0; i < nt; ++i) {
+      // Index entries of this warpgroup's next tile are fetched one tile ahead, so their
+      // latency hides behind the current tile.
+      const int i_first = ((t0 & 1) == wg) ? 0 : 1;
+      int n_row = 0, n_head = 0, n_slot = 0;
+      if (i_first < nt && i_first * kTile + r < c.n) {
+        const int e0 = i_first * kTile + r;
+        n_row = rows_i[e0]; n_head = heads_i[e0]; n_slot = slots_i[e0];
+      }
+      for (int i = i_first; i < nt; i += 2) {
         const int t = t0 + i;
-        if ((t & 1) != wg) continue;
         const uint32_t u = (uint32_t)t >> 1;
         const int e = i * kTile + r;
         const bool live = e < c.n;
-        const int row = live ? rows_i[e] : 0;
-        const int head = live ? heads_i[e] : 0;
-        const int slot = live ? slots_i[e] : 0;
+        const int row = n_row, head = n_head, slot = n_slot;
+        {
+          const int e2 = e + 2 * kTile;
+          const bool live2 = (i + 2 < nt) && e2 < c.n;
+          n_row = n_head = n_slot = 0;
+          if (live2) { n_row = ld_nc_pinned(rows_i + e2); n_head = ld_nc_pinned(heads_i + e2); n_slot = ld_nc_pinned(slots_i + e2); }
+        }
+        STAT_T0();
         int jmax = c.keys - 1;
         if (p.causal && live && (row - c.bos) / kTile == c.blk) jmax = min(jmax, row - c.key0);
 
-        mbar_wait(&bars->s_full[wg], u & 1, wc);
+        STAT_ADD(0); mbar_wait(&bars->s_full[wg], u & 1, wc); STAT_ADD(1);
         tc_fence_after();
         const uint32_t ts = tmem + lane_off + wg * 128;
-        uint32_t v[32];
-        float mx = -INFINITY;
-#pragma unroll 1
-        for (int ch = 0; ch < 4; ++ch) {
-          tmem_ld32(ts + ch * 32, v);
-          tmem_ld_wait();
+        // The whole 128-column row of S sits in registers: four loads in flight, one wait.
+        uint32_t v[128];
+        tmem_ld32(ts, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+        tmem_ld32(ts + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+        tmem_ld32(ts + 64, *reinterpret_cast<uint32_t(*)[32]>(&v[64]));
+        tmem_ld32(ts + 96, *reinterpret_cast<uint32_t(*)[32]>(&v[96]));
+        tmem_ld_wait();
+        if (jmax < kTile - 1) {                       // tail block or the query's own block: mask
 #pragma unroll
-          for (int k = 0; k < 32; ++k) {
-            const float s = __uint_as_float(v[k]);
-            mx = (ch * 32 + k <= jmax) ? fmaxf(mx, s) : mx;
-          }
+          for (int j = 0; j < kTile; ++j) v[j] = (j <= jmax) ? v[j] : 0xff800000u;   // -inf
         }
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int j = 0; j < kTile; j += 4) {
+#pragma unroll
+          for (int a = 0; a < 4; ++a) mx4[a] = fmaxf(mx4[a], __uint_as_float(v[j + a]));
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         const float m2 = mx * cs;
-        float l = 0.f;
-#pragma unroll 1
-        for (int ch = 0; ch < 4; ++ch) {
-          tmem_ld32(ts + ch * 32, v);
-          tmem_ld_wait();
-          unsigned char* dst_sub = myP + (ch >> 1) * kSub;
+        STAT_ADD(2);
+        float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            float pe[8];
+        for (int c16 = 0; c16 < 16; ++c16) {          // 16-byte chunks of the P row
+          float pe[8];
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              const int j = ch * 32 + g * 8 + k;
-              const float x = ex2(fmaf(__uint_as_float(v[g * 8 + k]), cs, -m2));
-              pe[k] = (j <= jmax) ? x : 0.f;
-              l += pe[k];
-            }
-            uint4 w;
-            w.x = pack2<T>(pe[0], pe[1]); w.y = pack2<T>(pe[2], pe[3]);
-            w.z = pack2<T>(pe[4], pe[5]); w.w = pack2<T>(pe[6], pe[7]);
-            *reinterpret_cast<uint4*>(dst_sub + swz128(r, (ch & 1) * 4 + g)) = w;
+          for (int k = 0; k < 8; ++k) {
+            pe[k] = ex2(fmaf(__uint_as_float(v[c16 * 8 + k]), cs, -m2));   // ex2(-inf) = 0 for masked keys
+            l4[k & 3] += pe[k];
           }
+          uint4 w;
+          w.x = pack2<T>(pe[0], pe[1]); w.y = pack2<T>(pe[2], pe[3]);
+          w.z = pack2<T>(pe[4], pe[5]); w.w = pack2<T>(pe[6], pe[7]);
+          *reinterpret_cast<uint4*>(myP + (c16 >> 3) * kSub + swz128(r, c16 & 7)) = w;
         }
+        const float l = (l4[0] + l4[1]) + (l4[2] + l4[3]);
+        STAT_ADD(3);
         fence_proxy_async();
         tc_fence_before();
         mbar_arrive(&bars->p_full[wg]);
 
         // ---- epilogue of the same tile ----
-        mbar_wait(&bars->o_full[wg], u & 1, wc);
+        STAT_ADD(4); mbar_wait(&bars->o_full[wg], u & 1, wc); STAT_ADD(5);
         tc_fence_after();
         const uint32_t to = tmem + lane_off + 256 + wg * D;
         const float inv = 1.f / l;
         const size_t dst_row = ((c.b * p.q_heads + head) * p.tokens + row) * (size_t)p.slots + slot;
         TP* dst = part_o + dst_row * D;
-#pragma unroll 1
-        for (int ch = 0; ch < D / 32; ++ch) {
-          tmem_ld32(to + ch * 32, v);
-          tmem_ld_wait();
-          if (live) {
-            if (sizeof(TP) == 2) {
-              uint4* d4 = reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(dst) + ch * 64);
 #pragma unroll
-              for (int g = 0; g < 4; ++g) {
-                uint4 w;
-                w.x = pack2<T>(__uint_as_float(v[g * 8 + 0]) * inv, __uint_as_float(v[g * 8 + 1]) * inv);
-                w.y = pack2<T>(__uint_as_float(v[g * 8 + 2]) * inv, __uint_as_float(v[g * 8 + 3]) * inv);
-                w.z = pack2<T>(__uint_as_float(v[g * 8 + 4]) * inv, __uint_as_float(v[g * 8 + 5]) * inv);
-                w.w = pack2<T>(__uint_as_float(v[g * 8 + 6]) * inv, __uint_as_float(v[g * 8 + 7]) * inv);
-                d4[g] = w;
-              }
-            } else {
-              float4* d4 = reinterpret_cast<float4*>(reinterpret_cast<unsigned char*>(dst) + ch * 128);
-#pragma unroll
-              for (int g = 0; g < 8; ++g)
-                d4[g] = make_float4(__uint_as_float(v[g * 4 + 0]) * inv, __uint_as_float(v[g * 4 + 1]) * inv,
-                                    __uint_as_float(v[g * 4 + 2]) * inv, __uint_as_float(v[g * 4 + 3]) * inv);
-            }
-          }
-        }
-        if (live) part_lse[dst_row] = m2 + log2f(l);
+        for (int ch = 0; ch < D / 32; ++ch) tmem_ld32(to + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[ch * 32]));
+        tmem_ld_wait();
         tc_fence_before();
-        mbar_arrive(&bars->so_free[wg]);
+        mbar_arrive(&bars->so_free[wg]);               // S and O columns of this buffer are free again
+        STAT_ADD(6);
+        if (live) part_lse[dst_row] = m2 + log2f(l);
+        if (sizeof(TP) == 2) {
+          // Stores of one row per thread would touch 32 different lines per instruction.
+          // Stage the 16-bit tile in this warpgroup's P buffer (its MMA has retired) and
+          // let eight (D=64) or sixteen (D=128) adjacent lanes write each row.
+          unsigned char* stage = myP;                  // [128 rows][D/64 x 128 bytes], swizzled per 128 B
+#pragma unroll
+          for (int g = 0; g < D / 8; ++g) {
+            uint4 w;
+            w.x = pack2<T>(__uint_as_float(v[g * 8 + 0]) * inv, __uint_as_float(v[g * 8 + 1]) * inv);
+            w.y = pack2<T>(__uint_as_float(v[g * 8 + 2]) * inv, __uint_as_float(v[g * 8 + 3]) * inv);
+            w.z = pack2<T>(__uint_as_float(v[g * 8 + 4]) * inv, __uint_as_float(v[g * 8 + 5]) * inv);
+            w.w = pack2<T>(__uint_as_float(v[g * 8 + 6]) * inv, __uint_as_float(v[g * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(stage + (g >> 3) * kSub + swz128(r, g & 7)) = w;
+          }
+          bars->out_ptr[wg][r] = live ? reinterpret_cast<unsigned char*>(dst) : nullptr;
+          STAT_ADD(7);
+          asm volatile("bar.sync %0, 128;" ::"r"(2 + wg) : "memory");
+          STAT_ADD(8);
+          constexpr int CPRO = D / 8;                  // 16-byte chunks per output row
+          constexpr int RPPO = 128 / CPRO;             // rows per pass of the warpgroup
+          const int tid = (warp & 3) * 32 + lane;
+          const int cc = tid % CPRO;
+#pragma unroll
+          for (int pass = 0; pass < CPRO; ++pass) {
+            const int rr = pass * RPPO + tid / CPRO;
+            unsigned char* op = bars->out_ptr[wg][rr];
+            const uint4 w = *reinterpret_cast<const uint4*>(stage + (cc >> 3) * kSub + swz128(rr, cc & 7));
+            if (op != nullptr) *reinterpret_cast<uint4*>(op + cc * 16) = w;
+          }
+          STAT_ADD(9);
+          asm volatile("bar.sync %0, 128;" ::"r"(2 + wg) : "memory");   // staging is P again from here on
+          STAT_ADD(10);
+        } else if (live) {
+          float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+          for (int g = 0; g < D / 4; ++g)
+            d4[g] = make_float4(__uint_as_float(v[g * 4 + 0]) * inv, __uint_as_float(v[g * 4 + 1]) * inv,
+                                __uint_as_float(v[g * 4 + 2]) * inv, __uint_as_float(v[g * 4 + 3]) * inv);
+        }
       }
       t0 += nt;
     }
@@ -312,83 +357,93 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
     __syncwarp();
   } else {
     // ============================ query gatherers ============================
-    const int pt = threadIdx.x - kGatherWarp0 * 32;      // 0..127
+    const int pt = threadIdx.x - kGatherWarp0 * 32;      // 0..63
     constexpr int CPR = D / 8;                            // 16-byte chunks per row
-    constexpr int RPP = 128 / CPR;                        // rows per pass
-    uint32_t t = 0, it_cnt = 0, pt_cnt = 0;
-    int pending = -1;                                     // stage whose copies are in flight
+    constexpr int RPP = kGatherThreads / CPR;             // rows per pass
+    constexpr int PASSES = kTile / RPP;
+    constexpr int LAG = NQ - 1;                           // tiles whose copies stay in flight
+    uint32_t t = 0, it_cnt = 0;
+    uint32_t issued = 0, arrived = 0;                     // tiles copied / published so far
+    auto publish_all = [&]() {
+      if (issued > arrived) {
+        cp_async_wait<0>();
+        fence_proxy_async();
+        for (; arrived < issued; ++arrived) mbar_arrive(&bars->q_full[arrived % NQ]);
+      }
+    };
     for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
       Column c;
       if (!load_column(c, item, ix, p, cu, n_kv_rows)) continue;
       const int nt = (c.n + kTile - 1) / kTile;
       if (c.keys < kTile) {
-        // Publish the previous column's last tile first: the K load awaited below is
-        // issued only after that tile's MMA has run.
-        if (pending >= 0) {
-          cp_async_wait<0>();
-          fence_proxy_async();
-          mbar_arrive(&bars->q_full[pending]);
-          pending = -1;
-        }
+        // Publish the previous column's tiles first: the K load awaited below is issued
+        // only after their MMAs have run.
+        publish_all();
         // zero the rows of K and V past the end of the sequence (they belong to the next one)
         const int dead = kTile - c.keys;
         mbar_wait(&bars->k_full, it_cnt & 1, wc);
-        for (int i = pt; i < dead * 8 * Cfg::kSubs; i += 128) {
+        for (int i = pt; i < dead * 8 * Cfg::kSubs; i += kGatherThreads) {
           const int s = i / (dead * 8), rr = c.keys + (i % (dead * 8)) / 8, ch = i % 8;
           *reinterpret_cast<uint4*>(sK + s * kSub + rr * 128 + ch * 16) = make_uint4(0, 0, 0, 0);
         }
         fence_proxy_async();
         mbar_arrive(&bars->k_fix);
         mbar_wait(&bars->v_full, it_cnt & 1, wc);
-        for (int i = pt; i < dead * 8 * Cfg::kSubs; i += 128) {
+        for (int i = pt; i < dead * 8 * Cfg::kSubs; i += kGatherThreads) {
           const int s = i / (dead * 8), rr = c.keys + (i % (dead * 8)) / 8, ch = i % 8;
           *reinterpret_cast<uint4*>(sV + s * kSub + rr * 128 + ch * 16) = make_uint4(0, 0, 0, 0);
         }
         fence_proxy_async();
         mbar_arrive(&bars->v_fix);
-        ++pt_cnt;
       }
       const int32_t* rows_i = ix.row_indices + (size_t)c.kv_row * ix.capacity + c.lo;
       const int32_t* heads_i = ix.head_indices + (size_t)c.kv_row * ix.capacity + c.lo;
       for (int i = 0; i < nt; ++i, ++t) {
         const uint32_t qs = t % NQ, uq = t / NQ;
-        const int e = i * kTile + pt;
-        const void* src = nullptr;
-        if (e < c.n) src = q + ((c.b * p.tokens + rows_i[e]) * p.q_heads + heads_i[e]) * (size_t)D;
+        const void* src[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int e = i * kTile + pt + h * kGatherThreads;
+          src[h] = nullptr;
+          if (e < c.n) src[h] = q + ((c.b * p.tokens + rows_i[e]) * p.q_heads + heads_i[e]) * (size_t)D;
+        }
         if (uq >= 1) mbar_wait(&bars->q_empty[qs], (uq - 1) & 1, wc);
-        bars->row_ptr[pt] = src;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const void** ptrs = bars->row_ptr[t & 1];          // double-buffered: one barrier per tile
+        ptrs[pt] = src[0];
+        ptrs[pt + kGatherThreads] = src[1];
+        asm volatile("bar.sync 1, 64;" ::: "memory");
         const uint32_t stage = smem_u32(sQ) + qs * Cfg::kOperand;
         const int cc = pt % CPR;
 #pragma unroll
-        for (int pass = 0; pass < CPR; ++pass) {
+        for (int pass = 0; pass < PASSES; ++pass) {
           const int rr = pass * RPP + pt / CPR;
-          const unsigned char* sp = static_cast<const unsigned char*>(bars->row_ptr[rr]);
+          const unsigned char* sp = static_cast<const unsigned char*>(ptrs[rr]);
           const uint32_t dst = stage + (cc >> 3) * kSub + swz128(rr, cc & 7);
           cp_async16(dst, sp ? sp + cc * 16 : static_cast<const void*>(q), sp ? 16u : 0u);
         }
         cp_async_commit();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (pending >= 0) {
-          cp_async_wait<1>();
+        ++issued;
+        if (issued - arrived > LAG) {                      // publish the oldest tile in flight
+          cp_async_wait<LAG>();
           fence_proxy_async();
-          mbar_arrive(&bars->q_full[pending]);
+          mbar_arrive(&bars->q_full[arrived % NQ]);
+          ++arrived;
         }
-        pending = (int)qs;
       }
       ++it_cnt;
     }
-    if (pending >= 0) {
-      cp_async_wait<0>();
-      fence_proxy_async();
-      mbar_arrive(&bars->q_full[pending]);
-    }
-    (void)pt_cnt;
+    publish_all();
   }
 
   tc_fence_before();
   __syncthreads();
   if (warp == kMmaWarp) tmem_dealloc(tmem, 512);
+#ifdef MOBA_WAIT_STATS
+  if (threadIdx.x < 16) {
+    unsigned long long* out = reinterpret_cast<unsigned long long*>(error_word + 64) + blockIdx.x * 16;
+    out[threadIdx.x] = (threadIdx.x == 15) ? (unsigned long long)(clock64() - kernel_t0) : bars->stats[threadIdx.x];
+  }
+#endif
 }
 
 template <int D, typename T, typename TP>

@@ -102,6 +102,14 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// A global load the compiler may not move: used to fetch index entries a tile or two before
+// they are needed (a plain load may be sunk to its first use, which defeats the prefetch).
+__device__ __forceinline__ int ld_nc_pinned(const int32_t* p) {
+  int v;
+  asm volatile("ld.global.nc.b32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+
 // ---------------------------------------------------------------------------
 // TMA tile loads (no multicast anywhere in this engine)
 // ---------------------------------------------------------------------------
