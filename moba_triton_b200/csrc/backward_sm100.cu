@@ -36,7 +36,7 @@ template <int D> struct BwdCfg {
   static constexpr int kKvBufs = (D == 64) ? 2 : 1;
   static constexpr int kPBytes = 2 * kSub;
   static constexpr int kSmemData = 2 * kKvBufs * kOperand + 2 * kStages * kOperand + 2 * kPBytes;
-  static constexpr int kSmem = kSmemData + 1024 + 2048;
+  static constexpr int kSmem = kSmemData + 1024 + 4096;
 };
 
 struct Bars {
@@ -45,6 +45,7 @@ struct Bars {
   uint64_t sp_full, pds_full, dq_full, dq_read, acc_full, acc_read;
   uint32_t tmem_base;
   int abort;
+  unsigned char* out_ptr[kTile];            // destination dQ rows of the tile being stored
   long long row_off[kTile];                 // element offset of the gathered row in q / dout, -1 = dead
 };
 
@@ -234,16 +235,43 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         // ---- dQ rows of this tile: this warpgroup stores columns [wg D/2, (wg+1) D/2) ----
         mbar_wait(&bars->dq_full, t & 1, wc);
         tc_fence_after();
-        unsigned char* dst = reinterpret_cast<unsigned char*>(
-            dq_part + ((qrow * p.slots) + slot) * (size_t)D + wg * (D / 2));
+        // Stage the 16-bit dQ tile in the P buffer (the MMAs that read it have retired) so
+        // that eight or sixteen adjacent lanes write each row; one row per thread straight to
+        // global memory would touch 32 lines per instruction.
 #pragma unroll 1
         for (int ch = 0; ch < D / 64; ++ch) {
           tmem_ld32(tmem + lane_off + cDQ + wg * (D / 2) + ch * 32, sv);
           tmem_ld_wait();
-          if (live) store_row32<T>(dst + ch * 64, sv, softmax_scale);
+          const int c16 = wg * (D / 16) + ch * 4;          // first 16-byte chunk of these 32 columns
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 w;
+            w.x = pack2<T>(__uint_as_float(sv[g * 8 + 0]) * softmax_scale, __uint_as_float(sv[g * 8 + 1]) * softmax_scale);
+            w.y = pack2<T>(__uint_as_float(sv[g * 8 + 2]) * softmax_scale, __uint_as_float(sv[g * 8 + 3]) * softmax_scale);
+            w.z = pack2<T>(__uint_as_float(sv[g * 8 + 4]) * softmax_scale, __uint_as_float(sv[g * 8 + 5]) * softmax_scale);
+            w.w = pack2<T>(__uint_as_float(sv[g * 8 + 6]) * softmax_scale, __uint_as_float(sv[g * 8 + 7]) * softmax_scale);
+            *reinterpret_cast<uint4*>(sP + ((c16 + g) >> 3) * kSub + swz128(r, (c16 + g) & 7)) = w;
+          }
         }
         tc_fence_before();
-        mbar_arrive(&bars->dq_read);
+        mbar_arrive(&bars->dq_read);                     // S / dQ columns may be overwritten
+        if (wg == 0) bars->out_ptr[r] = live ? reinterpret_cast<unsigned char*>(
+                                                   dq_part + ((qrow * p.slots) + slot) * (size_t)D) : nullptr;
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+        {
+          constexpr int CPRO = D / 8;                    // 16-byte chunks per row
+          constexpr int RPPO = 256 / CPRO;               // rows per pass of the 256 threads
+          const int tid = wg * 128 + r;
+          const int cc = tid % CPRO;
+#pragma unroll
+          for (int pass = 0; pass < kTile / RPPO; ++pass) {
+            const int rr = pass * RPPO + tid / CPRO;
+            unsigned char* op = bars->out_ptr[rr];
+            const uint4 w = *reinterpret_cast<const uint4*>(sP + (cc >> 3) * kSub + swz128(rr, cc & 7));
+            if (op != nullptr) *reinterpret_cast<uint4*>(op + cc * 16) = w;
+          }
+        }
+        asm volatile("bar.sync 2, 256;" ::: "memory");   // the staging area is P again
         row = row1; head = head1; slot = slot1; lse_r = lse_n; delta_r = delta_n;
         row1 = row2; head1 = head2; slot1 = slot2;
       }
