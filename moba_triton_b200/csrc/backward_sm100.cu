@@ -70,6 +70,13 @@ __device__ __forceinline__ bool load_column(Column& c, int item, const moba_b200
   return c.n > 0 && c.keys > 0;
 }
 
+// The work list is sorted longest first; CTAs take it in alternating direction
+// (0..G-1, G-1..0, ...) so that no CTA collects the largest column of every round.
+__device__ __forceinline__ int snake_item(int round) {
+  const int g = (int)gridDim.x, c = (int)blockIdx.x;
+  return round * g + ((round & 1) ? (g - 1 - c) : c);
+}
+
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -157,7 +164,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
     const int r = (warp & 3) * 32 + lane;              // tile row == TMEM lane
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     uint32_t t = 0, it_cnt = 0;
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    for (int round = 0; round * (int)gridDim.x < n_items; ++round) {
+      const int item = snake_item(round);
+      if (item >= n_items) continue;
       Column c;
       const bool work = load_column(c, item, ix, p, cu, n_kv_rows);
       const int kvh = c.kv_row % p.kv_heads;
@@ -304,7 +313,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       const uint32_t id_dq = make_idesc(0, 128, D, 0, 1) | fbits;      // dQ
       const uint32_t aP = smem_u32(sP), aS = smem_u32(sS);
       uint32_t t = 0, it_cnt = 0, pt_cnt = 0;
-      for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+      for (int round = 0; round * (int)gridDim.x < n_items; ++round) {
+      const int item = snake_item(round);
+      if (item >= n_items) continue;
         Column c;
         if (!load_column(c, item, ix, p, cu, n_kv_rows)) continue;
         const int nt = (c.n + kTile - 1) / kTile;
@@ -363,7 +374,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
     // ============================ K/V TMA loader ============================
     if (lane == 0) {
       uint32_t it_cnt = 0;
-      for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+      for (int round = 0; round * (int)gridDim.x < n_items; ++round) {
+      const int item = snake_item(round);
+      if (item >= n_items) continue;
         Column c;
         if (!load_column(c, item, ix, p, cu, n_kv_rows)) continue;
         const int kvh = c.kv_row % p.kv_heads;
@@ -386,7 +399,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
     constexpr int CPR = D / 8, RPP = 128 / CPR;
     uint32_t t = 0, it_cnt = 0;
     int pending[2] = {-1, -1};                            // stages in flight, oldest first
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    for (int round = 0; round * (int)gridDim.x < n_items; ++round) {
+      const int item = snake_item(round);
+      if (item >= n_items) continue;
       Column c;
       if (!load_column(c, item, ix, p, cu, n_kv_rows)) continue;
       const int nt = (c.n + kTile - 1) / kTile;
