@@ -306,7 +306,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
     }
   } else if (warp == kMmaWarp) {
     // ============================== MMA issuer ==============================
-    if (lane == 0) {
+    {
+      const bool leader = elect_one();                 // all 32 lanes run the loop, one issues
       const uint32_t fbits = (fmt << 7) | (fmt << 10);
       const uint32_t id_s = make_idesc(0, 128, 128, 0, 0) | fbits;     // S, dP
       const uint32_t id_acc = make_idesc(0, 128, D, 1, 1) | fbits;     // dV, dK
@@ -335,35 +336,35 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
 #pragma unroll
           for (int ks = 0; ks < D / 16; ++ks) {
             const uint32_t o = (ks >> 2) * kSub + (ks & 3) * 32;
-            umma_f16(tmem + cS, make_sdesc(aQ + o, 16, 1024), make_sdesc(aK + o, 16, 1024), id_s, ks > 0);
+            if (leader) umma_f16(tmem + cS, make_sdesc(aQ + o, 16, 1024), make_sdesc(aK + o, 16, 1024), id_s, ks > 0);
           }
 #pragma unroll
           for (int ks = 0; ks < D / 16; ++ks) {
             const uint32_t o = (ks >> 2) * kSub + (ks & 3) * 32;
-            umma_f16(tmem + cDP, make_sdesc(aG + o, 16, 1024), make_sdesc(aV + o, 16, 1024), id_s, ks > 0);
+            if (leader) umma_f16(tmem + cDP, make_sdesc(aG + o, 16, 1024), make_sdesc(aV + o, 16, 1024), id_s, ks > 0);
           }
-          umma_commit(&bars->sp_full);
+          if (leader) umma_commit(&bars->sp_full);
 
           mbar_wait(&bars->pds_full, t & 1, wc);
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {            // 16 queries per step
-            umma_f16(tmem + cDV, make_sdesc(aP + ks * 2048, kSub, 1024), make_sdesc(aG + ks * 2048, kSub, 1024),
+            if (leader) umma_f16(tmem + cDV, make_sdesc(aP + ks * 2048, kSub, 1024), make_sdesc(aG + ks * 2048, kSub, 1024),
                      id_acc, (i > 0 || ks > 0));
           }
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
-            umma_f16(tmem + cDK, make_sdesc(aS + ks * 2048, kSub, 1024), make_sdesc(aQ + ks * 2048, kSub, 1024),
+            if (leader) umma_f16(tmem + cDK, make_sdesc(aS + ks * 2048, kSub, 1024), make_sdesc(aQ + ks * 2048, kSub, 1024),
                      id_acc, (i > 0 || ks > 0));
           }
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {            // 16 keys per step
-            umma_f16(tmem + cDQ, make_sdesc(aS + (ks >> 2) * kSub + (ks & 3) * 32, 16, 1024),
+            if (leader) umma_f16(tmem + cDQ, make_sdesc(aS + (ks >> 2) * kSub + (ks & 3) * 32, 16, 1024),
                      make_sdesc(aK + ks * 2048, kSub, 1024), id_dq, ks > 0);
           }
-          umma_commit(&bars->dq_full);
-          umma_commit(&bars->qd_empty[st]);
-          if (i == nt - 1) { umma_commit(&bars->acc_full); umma_commit(&bars->kv_free[kb]); }
+          if (leader) umma_commit(&bars->dq_full);
+          if (leader) umma_commit(&bars->qd_empty[st]);
+          if (i == nt - 1) { if (leader) umma_commit(&bars->acc_full); if (leader) umma_commit(&bars->kv_free[kb]); }
         }
         ++it_cnt;
         if (partial) ++pt_cnt;
