@@ -226,6 +226,7 @@ def cpu_sample(wl, sample_tokens):
     """One pass of the oracle over the first `sample_tokens` tokens of head 0 of the
     first sequence: gate + sparse forward + backward in float32 on all host threads."""
     from oracle import moba_oracle as orc
+    torch.set_num_threads(max(1, os.cpu_count() or 1))     # torchrun pins OMP_NUM_THREADS to 1
     s = min(sample_tokens, wl["seqlens"][0])
     g = torch.Generator().manual_seed(wl["seed"])
     d = wl["d"]
