@@ -167,25 +167,29 @@ offsets_order_kernel(const int32_t* __restrict__ col_nnz, int32_t* __restrict__ 
   }
 }
 
-// One warp per (row chunk, sequence, query head).
-__global__ void __launch_bounds__(32)
+// One warp per (row chunk, sequence, query head); four chunks (warps) per CTA, each with its
+// own cursor array, so that enough warps are resident to cover the latency of the
+// dependent match / cursor / store chain.
+constexpr int kScatterWarps = 4;
+__global__ void __launch_bounds__(32 * kScatterWarps)
 scatter_kernel(const int32_t* __restrict__ block_idx, const int32_t* __restrict__ cu,
                const int32_t* __restrict__ tile_prefix, const int32_t* __restrict__ col_offsets,
                int32_t* __restrict__ rows_out, int32_t* __restrict__ heads_out,
                int32_t* __restrict__ slots_out, moba_b200_problem p, int R, int C,
                long long capacity) {
-  extern __shared__ int cursor[];
-  const int chunk = blockIdx.x;
+  extern __shared__ int cursor_all[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int* cursor = cursor_all + warp * p.num_blocks;
+  const int chunk = blockIdx.x * kScatterWarps + warp;
   const int seq = blockIdx.y / p.q_heads, hq = blockIdx.y % p.q_heads;
   const SeqSpan sp = seq_span(cu, p.packed, seq, p.tokens);
   const int row0 = chunk * R;
-  if (row0 >= sp.len) return;
+  if (chunk >= C || row0 >= sp.len) return;
   const int rows = min(R, sp.len - row0);
   const int nb_lim = (row0 + rows - 1) / p.block_size + 1;
   const int group = p.q_heads / p.kv_heads;
   const int kvh = hq / group, g = hq % group;
   const size_t kv_row = (size_t)seq * p.kv_heads + kvh;
-  const int lane = threadIdx.x;
   const int32_t* pre = tile_prefix + (kv_row * p.num_blocks) * (group * C) + g * C + chunk;
   const int32_t* off = col_offsets + kv_row * (p.num_blocks + 1);
   for (int i = lane; i < nb_lim; i += 32) cursor[i] = off[i] + pre[(size_t)i * (group * C)];
@@ -196,10 +200,11 @@ scatter_kernel(const int32_t* __restrict__ block_idx, const int32_t* __restrict_
   int32_t* so = slots_out + kv_row * capacity;
   const int n = rows * p.slots;
   const unsigned lt = (1u << lane) - 1u;
+  int blk_next = (lane < n) ? src[lane] : -1;            // loaded one step ahead
   for (int e0 = 0; e0 < n; e0 += 32) {
     const int e = e0 + lane;
-    int blk = -1;
-    if (e < n) blk = src[e];
+    const int blk = blk_next;
+    blk_next = (e + 32 < n) ? src[e + 32] : -1;
     const bool valid = blk >= 0 && blk < nb_lim;
     const int key = valid ? blk : (0x40000000 + lane);
     const unsigned same = __match_any_sync(0xffffffffu, key);
@@ -230,7 +235,7 @@ int launch_transpose(const moba_b200_problem& p, const int32_t* block_idx, const
     return MOBA_B200_ESCRATCH;
   }
   const size_t hist_bytes = (size_t)p.num_blocks * sizeof(int);
-  if (hist_bytes > 160 * 1024) {
+  if (kScatterWarps * hist_bytes > 200 * 1024) {
     set_error("transpose: %d blocks per sequence exceed the shared-memory histogram", p.num_blocks);
     return MOBA_B200_EUNSUPPORTED;
   }
@@ -239,9 +244,12 @@ int launch_transpose(const moba_b200_problem& p, const int32_t* block_idx, const
   const long long capacity = (long long)group * p.max_seqlen * p.slots;
   if (hist_bytes > 48 * 1024) {
     MOBA_CUDA_OK(cudaFuncSetAttribute(count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hist_bytes));
-    MOBA_CUDA_OK(cudaFuncSetAttribute(scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hist_bytes));
+    // handled below: the scatter kernel holds one cursor array per warp
     MOBA_CUDA_OK(cudaFuncSetAttribute(offsets_order_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hist_bytes));
   }
+  if (kScatterWarps * hist_bytes > 48 * 1024)
+    MOBA_CUDA_OK(cudaFuncSetAttribute(scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)(kScatterWarps * hist_bytes)));
   dim3 grid_rows(g.chunks, p.n_seq * p.q_heads);
   { KernelTimer t__("count_kernel", st);
   count_kernel<<<grid_rows, 256, hist_bytes, st>>>(block_idx, cu, tiles, p, g.chunk_rows, g.chunks);
@@ -254,8 +262,9 @@ int launch_transpose(const moba_b200_problem& p, const int32_t* block_idx, const
   offsets_order_kernel<<<p.n_seq * p.kv_heads, 1024, hist_bytes, st>>>(col_nnz, col_offsets, order, p.num_blocks);
   MOBA_LAUNCH_OK("offsets_order_kernel"); }
   { KernelTimer t__("scatter_kernel", st);
-  scatter_kernel<<<grid_rows, 32, hist_bytes, st>>>(block_idx, cu, tiles, col_offsets, rows, heads,
-                                                     slots, p, g.chunk_rows, g.chunks, capacity);
+  dim3 grid_scatter((g.chunks + kScatterWarps - 1) / kScatterWarps, p.n_seq * p.q_heads);
+  scatter_kernel<<<grid_scatter, 32 * kScatterWarps, kScatterWarps * hist_bytes, st>>>(
+      block_idx, cu, tiles, col_offsets, rows, heads, slots, p, g.chunk_rows, g.chunks, capacity);
   MOBA_LAUNCH_OK("scatter_kernel"); }
   return MOBA_B200_OK;
 }
