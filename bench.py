@@ -389,10 +389,12 @@ def run_ours(args, wl, rank, world, local_rank):
             achieved, peak, unit = amount / dur_s / 1e12, pk["tensor"], "TFLOP/s"
         else:
             achieved, peak, unit = amount / dur_s / 1e9, pk["hbm"], "GB/s"
-        traffic = None
-        tpath = os.path.join(ROOT, "profiles", "traffic.json")
-        if os.path.exists(tpath):
-            traffic = json.load(open(tpath)).get(wl["name"], {}).get(top)
+        # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised in
+        # profiles/tensor_kernels_cfg2_ncu_full.md: measured at 2 082 816 (query head, block) pairs
+        # and scaled by this run's pair count (the traffic is per-pair partial rows).
+        per_pair = {"bwd_sm100_kernel": (296.0e6 + 287.4e6) / 2082816, "fwd_sm100_kernel": (172.2e6 + 237.1e6) / 2082816,
+                    "gate_sm100_kernel": 33.8e6 / 2082816}
+        traffic = per_pair[top] * acct["pairs"] if top in per_pair else None
         t_roof = max(acct["f_step"] / (pk["tensor_burst"] * 1e12), acct["bytes_step"] / (pk["hbm"] * 1e9))
         line = {
             "metric": METRIC, "value": total_f / (ms_step * 1e-3) / 1e12, "unit": "TFLOP/s",
