@@ -36,7 +36,7 @@ template <int D> struct BwdCfg {
   static constexpr int kKvBufs = (D == 64) ? 2 : 1;
   static constexpr int kPBytes = 2 * kSub;
   static constexpr int kSmemData = 2 * kKvBufs * kOperand + 2 * kStages * kOperand + 2 * kPBytes;
-  static constexpr int kSmem = kSmemData + 1024 + 4096;
+  static constexpr int kSmem = kSmemData + 1024 + 8192;
 };
 
 struct Bars {
@@ -45,6 +45,10 @@ struct Bars {
   uint64_t sp_full, pds_full, dq_full, dq_read, acc_full, acc_read;
   uint32_t tmem_base;
   int abort;
+  // Per gathered row of each stage, written by the gather warps before they publish the
+  // stage: {token row or -1, head << 8 | slot, lse, delta}. The elementwise warps never
+  // touch global memory for these.
+  int4 meta[2][kTile];
   unsigned char* out_ptr[kTile];            // destination dQ rows of the tile being stored
   long long row_off[kTile];                 // element offset of the gathered row in q / dout, -1 = dead
 };
@@ -178,35 +182,18 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         continue;
       }
       const int nt = (c.n + kTile - 1) / kTile;
-      const int32_t* rows_i = ix.row_indices + (size_t)c.kv_row * ix.capacity + c.lo;
-      const int32_t* heads_i = ix.head_indices + (size_t)c.kv_row * ix.capacity + c.lo;
-      const int32_t* slots_i = ix.slot_of_pair + (size_t)c.kv_row * ix.capacity + c.lo;
-      // Software pipeline over the column's tiles: the index entry is fetched two tiles
-      // ahead and the row's lse / delta one tile ahead, so neither load is waited for.
-      int row = 0, head = 0, slot = 0, row1 = 0, head1 = 0, slot1 = 0;
-      float lse_r = 0.f, delta_r = 0.f;
-      if (r < c.n) {
-        row = rows_i[r]; head = heads_i[r]; slot = slots_i[r];
-        const size_t qr = (c.b * p.q_heads + head) * p.tokens + row;
-        lse_r = lse[qr]; delta_r = delta[qr];
-      }
-      if (kTile + r < c.n) { row1 = rows_i[kTile + r]; head1 = heads_i[kTile + r]; slot1 = slots_i[kTile + r]; }
       for (int i = 0; i < nt; ++i, ++t) {
-        const int e = i * kTile + r;
-        const bool live = e < c.n;
+        // The stage's metadata was written before the gather warps published the stage, the
+        // MMA warp waited for that before issuing S / dP, and sp_full follows those MMAs.
+        mbar_wait(&bars->sp_full, t & 1, wc);
+        const int4 mt = bars->meta[t % NST][r];
+        const int row = mt.x < 0 ? 0 : mt.x, head = mt.y >> 8, slot = mt.y & 0xff;
+        const bool live = mt.x >= 0;
+        const float lse_r = __int_as_float(mt.z), delta_r = __int_as_float(mt.w);
         const size_t qrow = (c.b * p.q_heads + head) * p.tokens + row;
-        // issue the loads of the following tiles now; they are consumed at the bottom
-        float lse_n = 0.f, delta_n = 0.f;
-        int row2 = 0, head2 = 0, slot2 = 0;
-        if (e + kTile < c.n) {
-          const size_t qn = (c.b * p.q_heads + head1) * p.tokens + row1;
-          lse_n = lse[qn]; delta_n = delta[qn];
-        }
-        if (e + 2 * kTile < c.n) { row2 = rows_i[e + 2 * kTile]; head2 = heads_i[e + 2 * kTile]; slot2 = slots_i[e + 2 * kTile]; }
         int jmax = live ? c.keys - 1 : -1;             // dead rows contribute nothing
         if (p.causal && live && (row - c.bos) / kTile == c.blk) jmax = min(jmax, row - c.key0);
 
-        mbar_wait(&bars->sp_full, t & 1, wc);
         tc_fence_after();
         uint32_t sv[32], pv[32];
 #pragma unroll 1
@@ -281,8 +268,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
           }
         }
         asm volatile("bar.sync 2, 256;" ::: "memory");   // the staging area is P again
-        row = row1; head = head1; slot = slot1; lse_r = lse_n; delta_r = delta_n;
-        row1 = row2; head1 = head2; slot1 = slot2;
       }
       // ---- the column's dV (warpgroup 0) and dK (warpgroup 1), one key row per thread ----
       mbar_wait(&bars->acc_full, it_cnt & 1, wc);
@@ -434,15 +419,22 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       }
       const int32_t* rows_i = ix.row_indices + (size_t)c.kv_row * ix.capacity + c.lo;
       const int32_t* heads_i = ix.head_indices + (size_t)c.kv_row * ix.capacity + c.lo;
-      int n_row = 0, n_head = 0;                           // index entry of the next tile, fetched ahead
-      if (pt < c.n) { n_row = rows_i[pt]; n_head = heads_i[pt]; }
+      const int32_t* slots_i = ix.slot_of_pair + (size_t)c.kv_row * ix.capacity + c.lo;
+      int n_row = 0, n_head = 0, n_slot = 0;               // index entry of the next tile, fetched ahead
+      if (pt < c.n) { n_row = rows_i[pt]; n_head = heads_i[pt]; n_slot = slots_i[pt]; }
       for (int i = 0; i < nt; ++i, ++t) {
         const uint32_t st = t % NST, us = t / NST;
         const int e = i * kTile + pt;
         long long off = -1;
-        if (e < c.n) off = (long long)(((c.b * p.tokens + n_row) * p.q_heads + n_head) * (size_t)D);
-        if (e + kTile < c.n) { n_row = rows_i[e + kTile]; n_head = heads_i[e + kTile]; }
+        int4 mt = make_int4(-1, 0, 0, 0);
+        if (e < c.n) {
+          off = (long long)(((c.b * p.tokens + n_row) * p.q_heads + n_head) * (size_t)D);
+          const size_t qr = (c.b * p.q_heads + n_head) * p.tokens + n_row;
+          mt = make_int4(n_row, (n_head << 8) | n_slot, __float_as_int(lse[qr]), __float_as_int(delta[qr]));
+        }
+        if (e + kTile < c.n) { n_row = rows_i[e + kTile]; n_head = heads_i[e + kTile]; n_slot = slots_i[e + kTile]; }
         if (us >= 1) mbar_wait(&bars->qd_empty[st], (us - 1) & 1, wc);
+        bars->meta[st][pt] = mt;
         bars->row_off[pt] = off;
         asm volatile("bar.sync 1, 128;" ::: "memory");
         const uint32_t stage_q = smem_u32(sQ) + st * Cfg::kOperand;
