@@ -367,3 +367,15 @@ def test_no_host_synchronisation_on_the_hot_path(device):
     finally:
         torch.cuda.set_sync_debug_mode("default")
     torch.cuda.synchronize()
+
+
+def test_backend_adapter_runs_the_engine(device):
+    from moba_triton_b200.adapter import B200Backend
+    b = B200Backend()
+    cfg = moba.MoBAConfig(128, 4)
+    assert b.is_available(cfg) == (True, "")
+    q, k, v = _dev(*make_qkv((1, 1024, 2, 64), dtype=torch.bfloat16, seed=3), device=device)
+    out = b.forward(q, k, v, cfg)
+    assert torch.equal(out, moba.moba_forward(q, k, v, cfg))
+    assert torch.equal(b.forward_grad(q, k, v, cfg), out)
+    assert torch.equal(b.selection(q, k, cfg).cpu(), oracle_mask(q.cpu(), k.cpu(), cfg))

@@ -116,3 +116,15 @@ def test_product_never_imports_the_oracle():
         for f in files:
             if f.endswith((".py", ".cu", ".cuh")):
                 assert "oracle" not in open(os.path.join(base, f)).read().replace("the oracle uses", ""), f
+
+
+def test_backend_adapter_follows_the_reference_protocol_and_never_raises():
+    from moba_triton_b200.adapter import B200Backend
+    b = B200Backend()
+    assert b.name and b.vendored is False and b.computes_moba is True
+    for m in ("is_available", "forward", "forward_grad", "selection"):
+        assert callable(getattr(b, m))
+    ok, reason = b.is_available(moba.MoBAConfig(128, 8))
+    assert isinstance(ok, bool) and isinstance(reason, str)
+    if not torch.cuda.is_available():
+        assert not ok and reason                       # says why instead of raising
