@@ -60,7 +60,7 @@ struct Bars {
   int abort;
   Column cols[4];                          // ring: cols[i & 3] describes the CTA's i-th column; n < 0 ends the stream
   unsigned char* out_ptr[4][kTile];        // destination rows of the tile each warpgroup is storing
-  const void* row_ptr[2][kTile];           // gather sources of two consecutive tiles (nullptr = dead row)
+  alignas(16) int row_idx[2][kTile];       // rows of the [batch * tokens * heads] view of q, two consecutive tiles
 };
 
 __device__ __forceinline__ bool load_column(Column& c, int item, const moba_b200_index& ix,
@@ -98,7 +98,7 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) 
 template <int D, typename T, typename TP>
 __global__ void __launch_bounds__(FwdCfg<D>::kThreads, 1)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
-                 const T* __restrict__ q, moba_b200_index ix, const int32_t* __restrict__ cu,
+                 const __grid_constant__ CUtensorMap q_map, const T* __restrict__ q, moba_b200_index ix, const int32_t* __restrict__ cu,
                  TP* __restrict__ part_o, float* __restrict__ part_lse, moba_b200_problem p, int n_items,
                  unsigned* error_word) {
   using Cfg = FwdCfg<D>;
@@ -124,7 +124,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
     mbar_init(&bars->k_fix, kGatherThreads); mbar_init(&bars->v_fix, kGatherThreads);
     mbar_init(&bars->k_free, 1); mbar_init(&bars->v_free, 1);
     for (int i = 0; i < 4; ++i) {
-      mbar_init(&bars->q_full[i], kGatherThreads); mbar_init(&bars->q_empty[i], 1);
+      mbar_init(&bars->q_full[i], 1); mbar_init(&bars->q_empty[i], 1);
       mbar_init(&bars->s_full[i], 1); mbar_init(&bars->p_full[i], 128);
       mbar_init(&bars->o_full[i], 1); mbar_init(&bars->so_free[i], 128);
       mbar_init(&bars->col_full[i], 1);
@@ -133,7 +133,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
     fence_barrier_init();
   }
   if (warp == Cfg::kMmaWarp) tmem_alloc(&bars->tmem_base, 512);
-  if (warp == Cfg::kLoadWarp && lane == 0) { tma_prefetch_desc(&k_map); tma_prefetch_desc(&v_map); }
+  if (warp == Cfg::kLoadWarp && lane == 0) { tma_prefetch_desc(&k_map); tma_prefetch_desc(&v_map); tma_prefetch_desc(&q_map); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -398,33 +398,21 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
   }
   else {
     // ============================ query gatherers ============================
+    // The Q rows of a tile come by TMA (tile::gather4: four rows per instruction); the two
+    // warps resolve the rows (two per thread, fetched a tile ahead) and issue the requests,
+    // whose bytes are counted on q_full. Rows past the end of a column are asked for
+    // outside the tensor and read as zeros.
     const int pt = threadIdx.x - Cfg::kGatherWarp0 * 32;  // 0..63
-    constexpr int CPR = D / 8;                            // 16-byte chunks per row
-    constexpr int RPP = kGatherThreads / CPR;             // rows per pass
-    constexpr int PASSES = kTile / RPP;
-    constexpr int LAG = NQ - 1;                           // tiles whose copies stay in flight
+    const int oob_row = p.batch * p.tokens * p.q_heads;
     uint32_t t = 0;
-    uint32_t issued = 0, arrived = 0;                     // tiles copied / published so far
-    auto publish_all = [&]() {
-      if (issued > arrived) {
-        cp_async_wait<0>();
-        fence_proxy_async();
-        for (; arrived < issued; ++arrived) mbar_arrive(&bars->q_full[arrived % NQ]);
-      }
-    };
     for (uint32_t it = 0;; ++it) {
-      // Never block with copies unpublished: the next descriptor appears only after the
-      // MMAs that consume them have run.
-      if (!mbar_try_wait(&bars->col_full[it & 3], (it >> 2) & 1)) publish_all();
       mbar_wait(&bars->col_full[it & 3], (it >> 2) & 1, wc);
       const Column c = bars->cols[it & 3];
       if (c.n < 0) break;
       const int nt = (c.n + kTile - 1) / kTile;
       if (c.keys < kTile) {
         // The block is cut short by the end of its sequence: zero the rows of K and V past
-        // it (they belong to the next sequence). Publish outstanding tiles first; the K
-        // load awaited here is issued only after their MMAs have run.
-        publish_all();
+        // it (they belong to the next sequence).
         const int dead = kTile - c.keys;
         mbar_wait(&bars->k_full, it & 1, wc);
         for (int i = pt; i < dead * 8 * Cfg::kSubs; i += kGatherThreads) {
@@ -443,40 +431,33 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       }
       const int32_t* rows_i = ix.row_indices + (size_t)c.kv_row * ix.capacity + c.lo;
       const int32_t* heads_i = ix.head_indices + (size_t)c.kv_row * ix.capacity + c.lo;
+      int n_row[2] = {0, 0}, n_head[2] = {0, 0};         // index entries of the next tile, fetched ahead
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int e = pt + h * kGatherThreads;
+        if (e < c.n) { n_row[h] = ld_nc_pinned(rows_i + e); n_head[h] = ld_nc_pinned(heads_i + e); }
+      }
       for (int i = 0; i < nt; ++i, ++t) {
         const uint32_t qs = t % NQ, uq = t / NQ;
-        const void* src[2];
+        int* ridx = bars->row_idx[t & 1];                  // double-buffered: one barrier per tile
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int e = i * kTile + pt + h * kGatherThreads;
-          src[h] = nullptr;
-          if (e < c.n) src[h] = q + ((c.b * p.tokens + rows_i[e]) * p.q_heads + heads_i[e]) * (size_t)D;
+          ridx[pt + h * kGatherThreads] = e < c.n ? (int)((c.b * p.tokens + n_row[h]) * p.q_heads + n_head[h]) : oob_row;
+          if (e + kTile < c.n) { n_row[h] = ld_nc_pinned(rows_i + e + kTile); n_head[h] = ld_nc_pinned(heads_i + e + kTile); }
         }
         if (uq >= 1) mbar_wait(&bars->q_empty[qs], (uq - 1) & 1, wc);
-        const void** ptrs = bars->row_ptr[t & 1];          // double-buffered: one barrier per tile
-        ptrs[pt] = src[0];
-        ptrs[pt + kGatherThreads] = src[1];
+        if (pt == 0) mbar_expect_tx(&bars->q_full[qs], Cfg::kOperand);
         asm volatile("bar.sync 1, 64;" ::: "memory");
-        const uint32_t stage = smem_u32(sQ) + qs * Cfg::kOperand;
-        const int cc = pt % CPR;
-#pragma unroll
-        for (int pass = 0; pass < PASSES; ++pass) {
-          const int rr = pass * RPP + pt / CPR;
-          const unsigned char* sp = static_cast<const unsigned char*>(ptrs[rr]);
-          const uint32_t dst = stage + (cc >> 3) * kSub + swz128(rr, cc & 7);
-          cp_async16(dst, sp ? sp + cc * 16 : static_cast<const void*>(q), sp ? 16u : 0u);
-        }
-        cp_async_commit();
-        ++issued;
-        if (issued - arrived > LAG) {                      // publish the oldest tile in flight
-          cp_async_wait<LAG>();
-          fence_proxy_async();
-          mbar_arrive(&bars->q_full[arrived % NQ]);
-          ++arrived;
+        // thread pt: tile rows 4 (pt % 32) .. + 3, 64-column half pt / 32 (head_dim 128 only)
+        if (pt / 32 < Cfg::kSubs) {
+          const int r0 = (pt % 32) * 4, sub = pt / 32;
+          const int4 r4 = *reinterpret_cast<const int4*>(ridx + r0);
+          tma_gather4(sQ + qs * Cfg::kOperand + sub * kSub + r0 * 128, &q_map, &bars->q_full[qs], sub * 64, r4.x, r4.y,
+                      r4.z, r4.w);
         }
       }
     }
-    publish_all();
   }
 
   tc_fence_before();
@@ -485,7 +466,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
 }
 
 template <int D, typename T, typename TP>
-int launch_one(const moba_b200_problem& p, const CUtensorMap& km, const CUtensorMap& vm, const void* q,
+int launch_one(const moba_b200_problem& p, const CUtensorMap& km, const CUtensorMap& vm, const CUtensorMap& qm, const void* q,
                const moba_b200_index& ix, const int32_t* cu, void* part_o, float* part_lse, int n_items,
                unsigned* err, cudaStream_t st) {
   auto kern = fwd_sm100_kernel<D, T, TP>;
@@ -494,7 +475,7 @@ int launch_one(const moba_b200_problem& p, const CUtensorMap& km, const CUtensor
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = n_items < sms ? n_items : sms;
-  kern<<<grid, FwdCfg<D>::kThreads, FwdCfg<D>::kSmem, st>>>(km, vm, (const T*)q, ix, cu, (TP*)part_o, part_lse, p,
+  kern<<<grid, FwdCfg<D>::kThreads, FwdCfg<D>::kSmem, st>>>(km, vm, qm, (const T*)q, ix, cu, (TP*)part_o, part_lse, p,
                                                              n_items, err);
   MOBA_LAUNCH_OK("fwd_sm100_kernel");
   return MOBA_B200_OK;
@@ -505,7 +486,7 @@ int launch_one(const moba_b200_problem& p, const CUtensorMap& km, const CUtensor
 bool fwd_sm100_supported(const moba_b200_problem& p) {
   return (p.dtype == MOBA_B200_BF16 || p.dtype == MOBA_B200_F16) && p.block_size == 128 &&
          (p.head_dim == 64 || p.head_dim == 128) &&
-         (long long)p.batch * p.tokens < 0x7fffffffLL;
+         (long long)p.batch * p.tokens * p.q_heads < 0x7fffffffLL;
 }
 
 int launch_fwd_sm100(const moba_b200_problem& p, const void* q, const void* k, const void* v,
@@ -514,15 +495,17 @@ int launch_fwd_sm100(const moba_b200_problem& p, const void* q, const void* k, c
   KernelTimer timer__("fwd_sm100_kernel", st);
   unsigned* err = device_error_word();
   if (err == nullptr) { set_error("forward: no device error word"); return MOBA_B200_ECUDA; }
-  CUtensorMap km, vm;
+  CUtensorMap km, vm, qm;
   const uint64_t rows = (uint64_t)p.batch * p.tokens;
   int rc = encode_rows_map(&km, k, rows, p.kv_heads, p.head_dim, 128);
   if (rc) return rc;
   rc = encode_rows_map(&vm, v, rows, p.kv_heads, p.head_dim, 128);
   if (rc) return rc;
+  rc = encode_2d_map(&qm, q, rows * p.q_heads, p.head_dim, 1);         // rows gathered four at a time
+  if (rc) return rc;
   const int n_items = p.num_blocks * p.n_seq * p.kv_heads;
   const bool bf = p.dtype == MOBA_B200_BF16;
-#define GO(D, T, TP) return launch_one<D, T, TP>(p, km, vm, q, ix, cu, part_o, part_lse, n_items, err, st)
+#define GO(D, T, TP) return launch_one<D, T, TP>(p, km, vm, qm, q, ix, cu, part_o, part_lse, n_items, err, st)
   if (p.head_dim == 64) {
     if (bf) { if (p.part_f32) GO(64, __nv_bfloat16, float); else GO(64, __nv_bfloat16, __nv_bfloat16); }
     else { if (p.part_f32) GO(64, __half, float); else GO(64, __half, __half); }

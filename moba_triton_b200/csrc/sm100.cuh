@@ -58,27 +58,50 @@ struct WaitCtx {
 #endif
 };
 
-constexpr uint32_t kWaitTries = 1u << 22;   // each try suspends for a while in hardware
+constexpr long long kWaitCycles = 1ll << 31;   // about a second of SM clock
+constexpr uint32_t kSuspendNs = 4000;          // a try may sleep this long; completion wakes it at once
+
+// try_wait with a suspend-time hint: a waiting warp sleeps in hardware instead of taking
+// issue slots from the warps that do the work.
+__device__ __forceinline__ bool mbar_try_wait_sleep(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendNs)
+      : "memory");
+  return ok != 0;
+}
 
 // Waits for the phase with the given parity to complete. Returns false (and
 // latches the abort flag) if it gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, int site = 0) {
   if (*ctx.abort) return false;
-#ifdef MOBA_WAIT_STATS
   const long long t0__ = clock64();
-#endif
-  for (uint32_t i = 0; i < kWaitTries; ++i) {
-    if (mbar_try_wait(bar, parity)) {
+  for (;;) {
+    if (mbar_try_wait_sleep(bar, parity)) {
 #ifdef MOBA_WAIT_STATS
-      if (ctx.stats != nullptr) atomicAdd(&ctx.stats[site], (unsigned long long)(clock64() - t0__));
+      if (ctx.stats != nullptr && (threadIdx.x & 31) == 0) atomicAdd(&ctx.stats[site], (unsigned long long)(clock64() - t0__));
 #endif
       return true;
     }
-    if ((i & 1023u) == 1023u && *ctx.abort) return false;
+    if (*ctx.abort) return false;
+    if (clock64() - t0__ > kWaitCycles) break;
   }
   *ctx.abort = 1;
+  atomicCAS(ctx.error_word, 0u, ((unsigned)site << 8));   // the first wait that gave up names itself
   atomicOr(ctx.error_word, kErrWaitTimeout);
   return false;
+}
+
+// Bounded wait that ignores the abort flag: used on the way out of a kernel, for
+// asynchronous work that must have landed before the CTA may exit.
+__device__ __forceinline__ void mbar_wait_quiet(uint64_t* bar, uint32_t parity) {
+  const long long t0__ = clock64();
+  while (!mbar_try_wait_sleep(bar, parity))
+    if (clock64() - t0__ > kWaitCycles) return;
 }
 
 __device__ __forceinline__ void fence_barrier_init() {
@@ -110,6 +133,12 @@ __device__ __forceinline__ int ld_nc_pinned(const int32_t* p) {
   return v;
 }
 
+__device__ __forceinline__ float ld_nc_pinned_f(const float* p) {
+  float v;
+  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+
 // ---------------------------------------------------------------------------
 // TMA tile loads (no multicast anywhere in this engine)
 // ---------------------------------------------------------------------------
@@ -121,6 +150,18 @@ __device__ __forceinline__ void tma_load_3d(void* dst_smem, const CUtensorMap* m
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(smem_u32(dst_smem)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+// Four rows of a 2-D tensor (map with a box of one row) -> four consecutive 128-byte rows
+// of a swizzled tile. Rows outside the tensor read as zeros.
+__device__ __forceinline__ void tma_gather4(void* dst_smem, const CUtensorMap* m, uint64_t* bar, int col,
+                                            int r0, int r1, int r2, int r3) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(smem_u32(dst_smem)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(col), "r"(r0), "r"(r1),
+        "r"(r2), "r"(r3)
       : "memory");
 }
 

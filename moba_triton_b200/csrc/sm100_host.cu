@@ -72,7 +72,7 @@ int encode_kbar_map_impl(CUtensorMap* out, const void* base, uint64_t kv_rows, u
 
 // one word per device of this process, zero-initialised with the module
 #ifdef MOBA_WAIT_STATS
-__device__ unsigned g_error_word[64 + 2 * 16 * 160];      // debug builds: + per-CTA wait counters
+__device__ unsigned g_error_word[64 + 2 * 32 * 160];      // debug builds: + per-CTA wait counters
 #else
 __device__ unsigned g_error_word[1];
 #endif
@@ -96,7 +96,7 @@ extern "C" int moba_b200_debug_stats(unsigned long long* host_out, int n_ctas) {
   unsigned* base = device_error_word();
   if (base == nullptr) return -1;
   cudaDeviceSynchronize();
-  return (int)cudaMemcpy(host_out, base + 64, (size_t)n_ctas * 16 * 8, cudaMemcpyDeviceToHost);
+  return (int)cudaMemcpy(host_out, base + 64, (size_t)n_ctas * 32 * 8, cudaMemcpyDeviceToHost);
 }
 #endif
 

@@ -101,4 +101,5 @@ def _device_error_word_stays_clear(request):
     yield
     if request.node.get_closest_marker("gpu") is not None and torch.cuda.is_available():
         from moba_triton_b200 import _lib
-        assert _lib.device_status() == 0, "a tensor-core kernel reported an error"
+        word = _lib.device_status()
+        assert word == 0, f"a tensor-core kernel reported an error (status word {word:#x})"
