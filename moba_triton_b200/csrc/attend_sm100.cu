@@ -56,6 +56,7 @@ struct Bars {
   uint64_t q_full[4], q_empty[4];
   uint64_t s_full[4], p_full[4], o_full[4], so_free[4];
   uint64_t col_full[4];                    // column descriptors published by the loader thread
+  uint64_t drain;                          // all MMAs of the CTA have completed
   uint32_t tmem_base;
   int abort;
   Column cols[4];                          // ring: cols[i & 3] describes the CTA's i-th column; n < 0 ends the stream
@@ -129,6 +130,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       mbar_init(&bars->o_full[i], 1); mbar_init(&bars->so_free[i], 128);
       mbar_init(&bars->col_full[i], 1);
     }
+    mbar_init(&bars->drain, 1);
     bars->abort = 0;
     fence_barrier_init();
   }
@@ -363,6 +365,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
           }
         }
       }
+      // Every MMA has completed before the CTA lets go of its TMEM, also on the way out of
+      // a run that gave up on a wait.
+      umma_commit(&bars->drain);
+      mbar_wait_quiet(&bars->drain, 0);
     }
     __syncwarp();
   } else if (warp == Cfg::kLoadWarp) {
@@ -379,6 +385,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         if (item >= n_items) continue;
         Column c;
         if (!load_column(c, item, ix, p, cu, n_kv_rows)) continue;
+        if (*wc.abort) break;                                 // no new loads once a wait gave up
         bars->cols[it_cnt & 3] = c;
         mbar_arrive(&bars->col_full[it_cnt & 3]);
         const int kvh = c.kv_row % p.kv_heads;
@@ -393,6 +400,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       }
       bars->cols[it_cnt & 3].n = -1;                          // end of the stream
       mbar_arrive(&bars->col_full[it_cnt & 3]);
+      // No load may be in flight into this CTA's shared memory when it exits.
+      if (it_cnt >= 1) {
+        mbar_wait_quiet(&bars->k_full, (it_cnt - 1) & 1);
+        mbar_wait_quiet(&bars->v_full, (it_cnt - 1) & 1);
+      }
     }
     __syncwarp();
   }
@@ -438,6 +450,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         if (e < c.n) { n_row[h] = ld_nc_pinned(rows_i + e); n_head[h] = ld_nc_pinned(heads_i + e); }
       }
       for (int i = 0; i < nt; ++i, ++t) {
+        if (*wc.abort) break;                              // no new requests once a wait gave up
         const uint32_t qs = t % NQ, uq = t / NQ;
         int* ridx = bars->row_idx[t & 1];                  // double-buffered: one barrier per tile
 #pragma unroll
@@ -457,6 +470,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
                       r4.z, r4.w);
         }
       }
+      if (*wc.abort) break;
+    }
+    // No request may be in flight into this CTA's shared memory when it exits.
+    for (uint32_t k = 0; k < (uint32_t)NQ && k < t; ++k) {
+      const uint32_t u = t - 1 - k;
+      mbar_wait_quiet(&bars->q_full[u % NQ], (u / NQ) & 1);
     }
   }
 

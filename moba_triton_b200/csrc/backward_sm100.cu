@@ -42,7 +42,7 @@ template <int D> struct BwdCfg {
 struct Bars {
   uint64_t k_full[2], v_full[2], kv_free[2], k_fix, v_fix;
   uint64_t qd_full[2], qd_empty[2];
-  uint64_t sp_full, pds_full, dq_full, dq_read, acc_full, acc_read;
+  uint64_t sp_full, pds_full, dq_full, dq_read, acc_full, acc_read, drain;
   uint32_t tmem_base;
   int abort;
   // Per gathered row of each stage, written by the gather warps before they publish the
@@ -146,7 +146,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
     mbar_init(&bars->k_fix, 128); mbar_init(&bars->v_fix, 128);
     mbar_init(&bars->sp_full, 1); mbar_init(&bars->pds_full, 256);
     mbar_init(&bars->dq_full, 1); mbar_init(&bars->dq_read, 256);
-    mbar_init(&bars->acc_full, 1); mbar_init(&bars->acc_read, 256);
+    mbar_init(&bars->acc_full, 1); mbar_init(&bars->acc_read, 256); mbar_init(&bars->drain, 1);
     bars->abort = 0;
     fence_barrier_init();
   }
@@ -354,6 +354,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         ++it_cnt;
         if (partial) ++pt_cnt;
       }
+      // Every MMA has completed before the CTA lets go of its TMEM, also on the way out of
+      // a run that gave up on a wait.
+      if (leader) umma_commit(&bars->drain);
+      mbar_wait_quiet(&bars->drain, 0);
     }
     __syncwarp();
   } else if (warp == kLoadWarp) {
@@ -365,6 +369,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       if (item >= n_items) continue;
         Column c;
         if (!load_column(c, item, ix, p, cu, n_kv_rows)) continue;
+        if (*wc.abort) break;                            // no new loads once a wait gave up
         const int kvh = c.kv_row % p.kv_heads;
         const int tok0 = (int)(c.b * p.tokens) + c.key0;
         const uint32_t kb = it_cnt % NKV, ku = it_cnt / NKV;
@@ -376,6 +381,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         for (int s = 0; s < Cfg::kSubs; ++s)
           tma_load_3d(sV + kb * Cfg::kOperand + s * kSub, &v_map, &bars->v_full[kb], s * 64, kvh, tok0);
         ++it_cnt;
+      }
+      // No load may be in flight into this CTA's shared memory when it exits.
+      for (uint32_t k = 1; k <= (uint32_t)NKV && k <= it_cnt; ++k) {
+        const uint32_t c = it_cnt - k;
+        mbar_wait_quiet(&bars->k_full[c % NKV], (c / NKV) & 1);
+        mbar_wait_quiet(&bars->v_full[c % NKV], (c / NKV) & 1);
       }
     }
     __syncwarp();

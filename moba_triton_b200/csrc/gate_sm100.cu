@@ -45,7 +45,7 @@ template <int D> struct GateCfg {
 };
 
 struct Bars {
-  uint64_t q_full, kb_full[2], kb_empty[2], s_full[2], s_free[2];
+  uint64_t q_full, kb_full[2], kb_empty[2], s_full[2], s_free[2], drain;
   uint32_t tmem_base;
   int abort;
 };
@@ -113,6 +113,7 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
       mbar_init(&bars->kb_full[i], 1); mbar_init(&bars->kb_empty[i], 1);
       mbar_init(&bars->s_full[i], 1); mbar_init(&bars->s_free[i], 128);
     }
+    mbar_init(&bars->drain, 1);
     bars->abort = 0;
     fence_barrier_init();
   }
@@ -161,11 +162,22 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             k2 = (col + 2 < cmax) ? k2 : 0u;
             k3 = (col + 3 < cmax) ? k3 : 0u;
           }
-          if (max(max(k0, k1), max(k2, k3)) > best[L - 1]) {
-            list_offer<L>(best, k0);
-            list_offer<L>(best, k1);
-            list_offer<L>(best, k2);
-            list_offer<L>(best, k3);
+          // Mostly at most one key of a group enters the list: offer the largest, and the
+          // other three only if one of them still beats the list's last entry. Keys are
+          // distinct (the column is in the low half), so exactly one equals the maximum.
+          const uint32_t m = max(max(k0, k1), max(k2, k3));
+          if (m > best[L - 1]) {
+            list_offer<L>(best, m);
+            k0 = (k0 == m) ? 0u : k0;
+            k1 = (k1 == m) ? 0u : k1;
+            k2 = (k2 == m) ? 0u : k2;
+            k3 = (k3 == m) ? 0u : k3;
+            if (max(max(k0, k1), max(k2, k3)) > best[L - 1]) {
+              list_offer<L>(best, k0);
+              list_offer<L>(best, k1);
+              list_offer<L>(best, k2);
+              list_offer<L>(best, k3);
+            }
           }
         }
       }
@@ -224,6 +236,10 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         umma_commit(&bars->s_full[st]);
         umma_commit(&bars->kb_empty[st]);
       }
+      // Every MMA has completed before the CTA lets go of its TMEM, also on the way out of
+      // a run that gave up on a wait.
+      umma_commit(&bars->drain);
+      mbar_wait_quiet(&bars->drain, 0);
     }
     __syncwarp();
   } else {
@@ -231,12 +247,21 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
       const int tok0 = (int)(b * p.tokens) + sp.bos + row0;
       mbar_expect_tx(&bars->q_full, Cfg::kOperand);
       for (int s = 0; s < Cfg::kSubs; ++s) tma_load_3d(sQ + s * kSub, &q_map, &bars->q_full, s * 64, hq, tok0);
+      int issued = 0;
       for (int c = 0; c < n_chunks; ++c) {
         const uint32_t st = c & 1, u = (uint32_t)c >> 1;
         if (u >= 1) mbar_wait(&bars->kb_empty[st], (u - 1) & 1, wc);
+        if (*wc.abort) break;                            // no new loads once a wait gave up
         mbar_expect_tx(&bars->kb_full[st], Cfg::kOperand);
         for (int s = 0; s < Cfg::kSubs; ++s)
           tma_load_3d(sKb + st * Cfg::kOperand + s * kSub, &kb_map, &bars->kb_full[st], s * 64, c * kTile, kv_row);
+        issued = c + 1;
+      }
+      // No load may be in flight into this CTA's shared memory when it exits.
+      mbar_wait_quiet(&bars->q_full, 0);
+      for (int k = 1; k <= 2 && k <= issued; ++k) {
+        const int c = issued - k;
+        mbar_wait_quiet(&bars->kb_full[c & 1], ((uint32_t)c >> 1) & 1);
       }
     }
     __syncwarp();
