@@ -32,7 +32,8 @@ namespace {
 
 constexpr int kTile = 128;                 // queries per tile == keys per block
 constexpr int kSub = kTile * 128;          // bytes of one [128 rows][64 elems] swizzled sub-tile
-constexpr int kGatherThreads = 64;         // two gather warps, two rows of a tile per thread
+constexpr int kGatherThreads = 64;         // two gather warps
+constexpr int kTmaRows = 84;               // rows of a tile fetched by TMA gather; the other 44 by 16-byte copies
 
 template <int D> struct FwdCfg {
   static constexpr int kSubs = D / 64;                 // sub-tiles per operand along the head dim
@@ -115,7 +116,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_kv_rows = p.n_seq * p.kv_heads;
 #ifdef MOBA_WAIT_STATS
-  const WaitCtx wc{&bars->abort, error_word, nullptr};
+  __shared__ unsigned long long wait_stats[32];
+  if (threadIdx.x < 32) wait_stats[threadIdx.x] = 0;
+  const long long kernel_t0 = clock64();
+  const WaitCtx wc{&bars->abort, error_word, wait_stats};
 #else
   const WaitCtx wc{&bars->abort, error_word};
 #endif
@@ -125,7 +129,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
     mbar_init(&bars->k_fix, kGatherThreads); mbar_init(&bars->v_fix, kGatherThreads);
     mbar_init(&bars->k_free, 1); mbar_init(&bars->v_free, 1);
     for (int i = 0; i < 4; ++i) {
-      mbar_init(&bars->q_full[i], 1); mbar_init(&bars->q_empty[i], 1);
+      mbar_init(&bars->q_full[i], 2); mbar_init(&bars->q_empty[i], 1);
       mbar_init(&bars->s_full[i], 1); mbar_init(&bars->p_full[i], 128);
       mbar_init(&bars->o_full[i], 1); mbar_init(&bars->so_free[i], 128);
       mbar_init(&bars->col_full[i], 1);
@@ -152,7 +156,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
     unsigned char* myP = sP + wg * Cfg::kPBytes;
     uint32_t t0 = 0;
     for (uint32_t it = 0;; ++it) {
-      mbar_wait(&bars->col_full[it & 3], (it >> 2) & 1, wc);
+      mbar_wait(&bars->col_full[it & 3], (it >> 2) & 1, wc, 1);
       const Column c = bars->cols[it & 3];
       if (c.n < 0) break;
       const int nt = (c.n + kTile - 1) / kTile;
@@ -181,7 +185,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         int jmax = c.keys - 1;
         if (p.causal && live && (row - c.bos) / kTile == c.blk) jmax = min(jmax, row - c.key0);
 
-        mbar_wait(&bars->s_full[wg], u & 1, wc);
+        mbar_wait(&bars->s_full[wg], u & 1, wc, 2);
         tc_fence_after();
         uint32_t v[32];
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -226,7 +230,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         const float inv = 1.f / l;
         const size_t dst_row = ((c.b * p.q_heads + head) * p.tokens + row) * (size_t)p.slots + slot;
         TP* dst = part_o + dst_row * D;
-        mbar_wait(&bars->o_full[wg], u & 1, wc);
+        mbar_wait(&bars->o_full[wg], u & 1, wc, 3);
         tc_fence_after();
 #pragma unroll 1
         for (int ch = 0; ch < D / 32; ++ch) {
@@ -390,10 +394,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         mbar_arrive(&bars->col_full[it_cnt & 3]);
         const int kvh = c.kv_row % p.kv_heads;
         const int tok0 = (int)(c.b * p.tokens) + c.key0;
-        if (it_cnt >= 1) mbar_wait(&bars->k_free, (it_cnt - 1) & 1, wc);
+        if (it_cnt >= 1) mbar_wait(&bars->k_free, (it_cnt - 1) & 1, wc, 4);
         mbar_expect_tx(&bars->k_full, Cfg::kOperand);
         for (int s = 0; s < Cfg::kSubs; ++s) tma_load_3d(sK + s * kSub, &k_map, &bars->k_full, s * 64, kvh, tok0);
-        if (it_cnt >= 1) mbar_wait(&bars->v_free, (it_cnt - 1) & 1, wc);
+        if (it_cnt >= 1) mbar_wait(&bars->v_free, (it_cnt - 1) & 1, wc, 5);
         mbar_expect_tx(&bars->v_full, Cfg::kOperand);
         for (int s = 0; s < Cfg::kSubs; ++s) tma_load_3d(sV + s * kSub, &v_map, &bars->v_full, s * 64, kvh, tok0);
         ++it_cnt;
@@ -410,30 +414,50 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
   }
   else {
     // ============================ query gatherers ============================
-    // The Q rows of a tile come by TMA (tile::gather4: four rows per instruction); the two
-    // warps resolve the rows (two per thread, fetched a tile ahead) and issue the requests,
-    // whose bytes are counted on q_full. Rows past the end of a column are asked for
-    // outside the tensor and read as zeros.
+    // A tile's Q rows arrive by two routes at once, because neither is fast enough alone
+    // (about 6 bytes per clock each): rows [0, kTmaRows) by TMA (tile::gather4, four rows
+    // per request, bytes counted on q_full), the rest by 16-byte asynchronous copies.
+    // Warp 0 resolves the rows (four per lane, fetched a tile ahead) and issues the TMA
+    // requests; warp 1 only copies, so that its waits for copies sit out no other load.
+    // Rows past the end of a column are asked for outside the tensor (TMA) or zero-filled.
+    const int gw = warp - Cfg::kGatherWarp0;
     const int pt = threadIdx.x - Cfg::kGatherWarp0 * 32;  // 0..63
     const int oob_row = p.batch * p.tokens * p.q_heads;
+    constexpr int CPR = D / 8;                            // 16-byte chunks per row
+    constexpr int RPI = 32 / CPR;                         // rows per copy instruction of the warp
+    constexpr int kCopyPasses = (kTile - kTmaRows) / RPI;
     uint32_t t = 0;
+    uint32_t issued = 0, arrived = 0;                     // warp 1: tiles copied / published so far
+    auto publish_all = [&]() {                            // warp 1: never block with copies unpublished
+      if (gw == 1 && issued > arrived) {
+        cp_async_wait<0>();
+        fence_proxy_async();
+        __syncwarp();
+        for (; arrived < issued; ++arrived)
+          if (lane == 0) mbar_arrive(&bars->q_full[arrived % NQ]);
+      }
+    };
     for (uint32_t it = 0;; ++it) {
-      mbar_wait(&bars->col_full[it & 3], (it >> 2) & 1, wc);
+      // The next descriptor appears only after MMAs that consume the copies have run.
+      if (gw == 1 && __shfl_sync(0xffffffffu, mbar_try_wait(&bars->col_full[it & 3], (it >> 2) & 1) ? 0 : 1, 0)) publish_all();
+      mbar_wait(&bars->col_full[it & 3], (it >> 2) & 1, wc, 6);
       const Column c = bars->cols[it & 3];
       if (c.n < 0) break;
       const int nt = (c.n + kTile - 1) / kTile;
       if (c.keys < kTile) {
         // The block is cut short by the end of its sequence: zero the rows of K and V past
-        // it (they belong to the next sequence).
+        // it (they belong to the next sequence). Outstanding copies go first; the K load
+        // awaited here is issued only after their MMAs have run.
+        publish_all();
         const int dead = kTile - c.keys;
-        mbar_wait(&bars->k_full, it & 1, wc);
+        mbar_wait(&bars->k_full, it & 1, wc, 7);
         for (int i = pt; i < dead * 8 * Cfg::kSubs; i += kGatherThreads) {
           const int s = i / (dead * 8), rr = c.keys + (i % (dead * 8)) / 8, ch = i % 8;
           *reinterpret_cast<uint4*>(sK + s * kSub + rr * 128 + ch * 16) = make_uint4(0, 0, 0, 0);
         }
         fence_proxy_async();
         mbar_arrive(&bars->k_fix);
-        mbar_wait(&bars->v_full, it & 1, wc);
+        mbar_wait(&bars->v_full, it & 1, wc, 8);
         for (int i = pt; i < dead * 8 * Cfg::kSubs; i += kGatherThreads) {
           const int s = i / (dead * 8), rr = c.keys + (i % (dead * 8)) / 8, ch = i % 8;
           *reinterpret_cast<uint4*>(sV + s * kSub + rr * 128 + ch * 16) = make_uint4(0, 0, 0, 0);
@@ -443,35 +467,62 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       }
       const int32_t* rows_i = ix.row_indices + (size_t)c.kv_row * ix.capacity + c.lo;
       const int32_t* heads_i = ix.head_indices + (size_t)c.kv_row * ix.capacity + c.lo;
-      int n_row[2] = {0, 0}, n_head[2] = {0, 0};         // index entries of the next tile, fetched ahead
+      int n_row[4] = {0, 0, 0, 0}, n_head[4] = {0, 0, 0, 0};   // warp 0: entries of rows 4 lane .. + 3 of the next tile
+      if (gw == 0) {
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int e = pt + h * kGatherThreads;
-        if (e < c.n) { n_row[h] = ld_nc_pinned(rows_i + e); n_head[h] = ld_nc_pinned(heads_i + e); }
+        for (int k = 0; k < 4; ++k) {
+          const int e = lane * 4 + k;
+          if (e < c.n) { n_row[k] = ld_nc_pinned(rows_i + e); n_head[k] = ld_nc_pinned(heads_i + e); }
+        }
       }
       for (int i = 0; i < nt; ++i, ++t) {
         if (*wc.abort) break;                              // no new requests once a wait gave up
         const uint32_t qs = t % NQ, uq = t / NQ;
         int* ridx = bars->row_idx[t & 1];                  // double-buffered: one barrier per tile
+        int r4[4] = {0, 0, 0, 0};
+        if (gw == 0) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int e = i * kTile + pt + h * kGatherThreads;
-          ridx[pt + h * kGatherThreads] = e < c.n ? (int)((c.b * p.tokens + n_row[h]) * p.q_heads + n_head[h]) : oob_row;
-          if (e + kTile < c.n) { n_row[h] = ld_nc_pinned(rows_i + e + kTile); n_head[h] = ld_nc_pinned(heads_i + e + kTile); }
+          for (int k = 0; k < 4; ++k) {
+            const int e = i * kTile + lane * 4 + k;
+            r4[k] = e < c.n ? (int)((c.b * p.tokens + n_row[k]) * p.q_heads + n_head[k]) : oob_row;
+            if (e + kTile < c.n) { n_row[k] = ld_nc_pinned(rows_i + e + kTile); n_head[k] = ld_nc_pinned(heads_i + e + kTile); }
+          }
+          *reinterpret_cast<int4*>(ridx + lane * 4) = make_int4(r4[0], r4[1], r4[2], r4[3]);
         }
-        if (uq >= 1) mbar_wait(&bars->q_empty[qs], (uq - 1) & 1, wc);
-        if (pt == 0) mbar_expect_tx(&bars->q_full[qs], Cfg::kOperand);
-        asm volatile("bar.sync 1, 64;" ::: "memory");
-        // thread pt: tile rows 4 (pt % 32) .. + 3, 64-column half pt / 32 (head_dim 128 only)
-        if (pt / 32 < Cfg::kSubs) {
-          const int r0 = (pt % 32) * 4, sub = pt / 32;
-          const int4 r4 = *reinterpret_cast<const int4*>(ridx + r0);
-          tma_gather4(sQ + qs * Cfg::kOperand + sub * kSub + r0 * 128, &q_map, &bars->q_full[qs], sub * 64, r4.x, r4.y,
-                      r4.z, r4.w);
+        if (uq >= 1) mbar_wait(&bars->q_empty[qs], (uq - 1) & 1, wc, 9);
+        if (pt == 0) mbar_expect_tx(&bars->q_full[qs], kTmaRows * D * 2);
+        asm volatile("bar.sync 1, 64;" ::: "memory");      // the row list of this tile is in shared memory
+        if (gw == 0) {
+          if (lane < kTmaRows / 4) {
+#pragma unroll
+            for (int sub = 0; sub < Cfg::kSubs; ++sub)
+              tma_gather4(sQ + qs * Cfg::kOperand + sub * kSub + lane * 512, &q_map, &bars->q_full[qs], sub * 64, r4[0],
+                          r4[1], r4[2], r4[3]);
+          }
+        } else {
+          const uint32_t stage = smem_u32(sQ) + qs * Cfg::kOperand;
+          const int cc = lane % CPR;
+#pragma unroll
+          for (int pass = 0; pass < kCopyPasses; ++pass) {
+            const int rr = kTmaRows + pass * RPI + lane / CPR;
+            const int ri = ridx[rr];
+            const bool live = ri != oob_row;
+            cp_async16(stage + (cc >> 3) * kSub + swz128(rr, cc & 7), q + (size_t)(live ? ri : 0) * D + cc * 8, live ? 16u : 0u);
+          }
+          cp_async_commit();
+          ++issued;
+          if (issued - arrived > 1) {                      // publish the older tile in flight
+            cp_async_wait<1>();
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->q_full[arrived % NQ]);
+            ++arrived;
+          }
         }
       }
       if (*wc.abort) break;
     }
+    publish_all();
     // No request may be in flight into this CTA's shared memory when it exits.
     for (uint32_t k = 0; k < (uint32_t)NQ && k < t; ++k) {
       const uint32_t u = t - 1 - k;
@@ -482,6 +533,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
   tc_fence_before();
   __syncthreads();
   if (warp == Cfg::kMmaWarp) tmem_dealloc(tmem, 512);
+#ifdef MOBA_WAIT_STATS
+  if (threadIdx.x < 32) {
+    unsigned long long* out = reinterpret_cast<unsigned long long*>(error_word + 64) + (size_t)blockIdx.x * 32;
+    out[threadIdx.x] = threadIdx.x == 31 ? (unsigned long long)(clock64() - kernel_t0) : wait_stats[threadIdx.x];
+  }
+#endif
 }
 
 template <int D, typename T, typename TP>
