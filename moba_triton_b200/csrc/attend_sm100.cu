@@ -9,7 +9,9 @@
 // only several chains side by side keep the SM busy.
 //   loader   (1 thread)  walks the work list, publishes each column's descriptor in
 //                        shared memory, TMA-loads its K block and V block
-//   gather   (2 warps)   cp.async: 128 selected query rows per tile -> swizzled smem
+//   gather   (2 warps)   128 selected query rows per tile -> swizzled smem, by TMA
+//                        tile::gather4 (warp 0, which resolves the rows) and by 16-byte
+//                        asynchronous copies (warp 1) side by side
 //   mma      (1 thread)  S = Q K^T (M128 N128 K=D), then O = P V (M128 N=D K128) written
 //                        over the first D columns of the same TMEM buffer
 //   softmax  (NB x 4 warps; warpgroup w owns tiles t = w mod NB) tcgen05.ld S,
@@ -32,19 +34,25 @@ namespace {
 
 constexpr int kTile = 128;                 // queries per tile == keys per block
 constexpr int kSub = kTile * 128;          // bytes of one [128 rows][64 elems] swizzled sub-tile
-constexpr int kGatherThreads = 64;         // two gather warps
-constexpr int kTmaRows = 84;               // rows of a tile fetched by TMA gather; the other 44 by 16-byte copies
 
 template <int D> struct FwdCfg {
   static constexpr int kSubs = D / 64;                 // sub-tiles per operand along the head dim
   static constexpr int kOperand = kSubs * kSub;        // bytes of K, V or one Q stage
-  static constexpr int kBufs = (D == 64) ? 4 : 2;      // tiles in flight (TMEM / P buffers, softmax warpgroups)
-  static constexpr int kQStages = (D == 64) ? 3 : 2;
+  // Tiles in flight (TMEM / P buffers, softmax warpgroups). At head_dim 64 twenty warps of 96
+  // registers fit: 4 warpgroups + 2 gather warps measured 0.45 ms at [1,131072,4,64] (the gather
+  // warps are the busy ones), 3 + 6 measured 0.49 ms (then the softmax warps are).
+  static constexpr int kBufs = (D == 64) ? 4 : 2;
+  static constexpr int kQStages = (D == 64) ? (kBufs >= 4 ? 3 : 4) : 2;
+  // Gather warps: warp 0 resolves rows and requests the first kTmaRows of a tile by TMA,
+  // the others share the 16-byte copies of the rest (a warp sustains ~3 B/clk of those).
+  static constexpr int kGatherWarps = 2;
+  static constexpr int kGatherThreads = 32 * kGatherWarps;
+  static constexpr int kTmaRows = 72;                  // 64 ... 104 measured; 72 (and 64) best
   static constexpr int kPBytes = 2 * kSub;             // [128][128] 16-bit
   static constexpr int kSmemData = 2 * kOperand + kQStages * kOperand + kBufs * kPBytes;
   static constexpr int kSmem = kSmemData + 1024 /*align*/ + 10240 /*barriers, pointers*/;
   static constexpr int kMmaWarp = 4 * kBufs, kLoadWarp = kMmaWarp + 1, kGatherWarp0 = kMmaWarp + 2;
-  static constexpr int kThreads = (4 * kBufs + 4) * 32;
+  static constexpr int kThreads = (4 * kBufs + 2 + kGatherWarps) * 32;
 };
 
 struct Column {                            // one unit of work
@@ -126,10 +134,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->k_full, 1); mbar_init(&bars->v_full, 1);
-    mbar_init(&bars->k_fix, kGatherThreads); mbar_init(&bars->v_fix, kGatherThreads);
+    mbar_init(&bars->k_fix, Cfg::kGatherThreads); mbar_init(&bars->v_fix, Cfg::kGatherThreads);
     mbar_init(&bars->k_free, 1); mbar_init(&bars->v_free, 1);
     for (int i = 0; i < 4; ++i) {
-      mbar_init(&bars->q_full[i], 2); mbar_init(&bars->q_empty[i], 1);
+      mbar_init(&bars->q_full[i], Cfg::kGatherWarps); mbar_init(&bars->q_empty[i], 1);
       mbar_init(&bars->s_full[i], 1); mbar_init(&bars->p_full[i], 128);
       mbar_init(&bars->o_full[i], 1); mbar_init(&bars->so_free[i], 128);
       mbar_init(&bars->col_full[i], 1);
@@ -418,18 +426,22 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
     // (about 6 bytes per clock each): rows [0, kTmaRows) by TMA (tile::gather4, four rows
     // per request, bytes counted on q_full), the rest by 16-byte asynchronous copies.
     // Warp 0 resolves the rows (four per lane, fetched a tile ahead) and issues the TMA
-    // requests; warp 1 only copies, so that its waits for copies sit out no other load.
+    // requests; the other warps only copy, so that their waits for copies sit out no other
+    // load.
     // Rows past the end of a column are asked for outside the tensor (TMA) or zero-filled.
     const int gw = warp - Cfg::kGatherWarp0;
-    const int pt = threadIdx.x - Cfg::kGatherWarp0 * 32;  // 0..63
+    const int pt = threadIdx.x - Cfg::kGatherWarp0 * 32;
+    constexpr int kTmaRows = Cfg::kTmaRows, kCopyWarps = Cfg::kGatherWarps - 1;
+    static_assert(kTmaRows % 4 == 0 && kTmaRows <= kTile, "TMA rows come four at a time");
     const int oob_row = p.batch * p.tokens * p.q_heads;
     constexpr int CPR = D / 8;                            // 16-byte chunks per row
     constexpr int RPI = 32 / CPR;                         // rows per copy instruction of the warp
     constexpr int kCopyPasses = (kTile - kTmaRows) / RPI;
     uint32_t t = 0;
-    uint32_t issued = 0, arrived = 0;                     // warp 1: tiles copied / published so far
-    auto publish_all = [&]() {                            // warp 1: never block with copies unpublished
-      if (gw == 1 && issued > arrived) {
+    static_assert((kTile - kTmaRows) % RPI == 0, "whole copy instructions");
+    uint32_t issued = 0, arrived = 0;                     // copying warps: tiles copied / published so far
+    auto publish_all = [&]() {                            // copying warps: never block with copies unpublished
+      if (gw >= 1 && issued > arrived) {
         cp_async_wait<0>();
         fence_proxy_async();
         __syncwarp();
@@ -439,7 +451,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
     };
     for (uint32_t it = 0;; ++it) {
       // The next descriptor appears only after MMAs that consume the copies have run.
-      if (gw == 1 && __shfl_sync(0xffffffffu, mbar_try_wait(&bars->col_full[it & 3], (it >> 2) & 1) ? 0 : 1, 0)) publish_all();
+      if (gw >= 1 && __shfl_sync(0xffffffffu, mbar_try_wait(&bars->col_full[it & 3], (it >> 2) & 1) ? 0 : 1, 0)) publish_all();
       mbar_wait(&bars->col_full[it & 3], (it >> 2) & 1, wc, 6);
       const Column c = bars->cols[it & 3];
       if (c.n < 0) break;
@@ -451,14 +463,14 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         publish_all();
         const int dead = kTile - c.keys;
         mbar_wait(&bars->k_full, it & 1, wc, 7);
-        for (int i = pt; i < dead * 8 * Cfg::kSubs; i += kGatherThreads) {
+        for (int i = pt; i < dead * 8 * Cfg::kSubs; i += Cfg::kGatherThreads) {
           const int s = i / (dead * 8), rr = c.keys + (i % (dead * 8)) / 8, ch = i % 8;
           *reinterpret_cast<uint4*>(sK + s * kSub + rr * 128 + ch * 16) = make_uint4(0, 0, 0, 0);
         }
         fence_proxy_async();
         mbar_arrive(&bars->k_fix);
         mbar_wait(&bars->v_full, it & 1, wc, 8);
-        for (int i = pt; i < dead * 8 * Cfg::kSubs; i += kGatherThreads) {
+        for (int i = pt; i < dead * 8 * Cfg::kSubs; i += Cfg::kGatherThreads) {
           const int s = i / (dead * 8), rr = c.keys + (i % (dead * 8)) / 8, ch = i % 8;
           *reinterpret_cast<uint4*>(sV + s * kSub + rr * 128 + ch * 16) = make_uint4(0, 0, 0, 0);
         }
@@ -491,7 +503,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         }
         if (uq >= 1) mbar_wait(&bars->q_empty[qs], (uq - 1) & 1, wc, 9);
         if (pt == 0) mbar_expect_tx(&bars->q_full[qs], kTmaRows * D * 2);
-        asm volatile("bar.sync 1, 64;" ::: "memory");      // the row list of this tile is in shared memory
+        asm volatile("bar.sync 1, %0;" ::"n"(Cfg::kGatherThreads) : "memory");   // the row list of this tile is in shared memory
         if (gw == 0) {
           if (lane < kTmaRows / 4) {
 #pragma unroll
@@ -503,7 +515,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
           const uint32_t stage = smem_u32(sQ) + qs * Cfg::kOperand;
           const int cc = lane % CPR;
 #pragma unroll
-          for (int pass = 0; pass < kCopyPasses; ++pass) {
+          for (int pass = gw - 1; pass < kCopyPasses; pass += kCopyWarps) {
             const int rr = kTmaRows + pass * RPI + lane / CPR;
             const int ri = ridx[rr];
             const bool live = ri != oob_row;
