@@ -200,25 +200,44 @@ scatter_kernel(const int32_t* __restrict__ block_idx, const int32_t* __restrict_
   int32_t* so = slots_out + kv_row * capacity;
   const int n = rows * p.slots;
   const unsigned lt = (1u << lane) - 1u;
-  int blk_next = (lane < n) ? src[lane] : -1;            // loaded one step ahead
-  for (int e0 = 0; e0 < n; e0 += 32) {
-    const int e = e0 + lane;
-    const int blk = blk_next;
-    blk_next = (e + 32 < n) ? src[e + 32] : -1;
-    const bool valid = blk >= 0 && blk < nb_lim;
-    const int key = valid ? blk : (0x40000000 + lane);
-    const unsigned same = __match_any_sync(0xffffffffu, key);
-    int base = 0;
-    if (valid) base = cursor[blk];
-    __syncwarp();
-    if (valid && (same & lt) == 0) cursor[blk] = base + __popc(same);
-    __syncwarp();
-    if (valid) {
-      const long long dst = base + __popc(same & lt);
-      if (dst < capacity) {
-        ro[dst] = sp.bos + row0 + e / p.slots;
-        ho[dst] = hq;
-        so[dst] = e % p.slots;
+  // The walk is one long dependent chain per warp (match, cursor, store), and few warps are
+  // resident when there are few heads, so the entries are fetched a batch of kBatch steps
+  // ahead: one memory latency per batch instead of one per step.
+  constexpr int kBatch = 8;
+  int nxt[kBatch];
+#pragma unroll
+  for (int j = 0; j < kBatch; ++j) {
+    const int e = j * 32 + lane;
+    nxt[j] = (e < n) ? src[e] : -1;
+  }
+  for (int e0 = 0; e0 < n; e0 += 32 * kBatch) {
+    int cur[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      cur[j] = nxt[j];
+      const int e = e0 + 32 * kBatch + j * 32 + lane;
+      nxt[j] = (e < n) ? src[e] : -1;
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int e = e0 + j * 32 + lane;
+      if (e0 + j * 32 >= n) break;                         // warp-uniform
+      const int blk = cur[j];
+      const bool valid = blk >= 0 && blk < nb_lim;
+      const int key = valid ? blk : (0x40000000 + lane);
+      const unsigned same = __match_any_sync(0xffffffffu, key);
+      int base = 0;
+      if (valid) base = cursor[blk];
+      __syncwarp();
+      if (valid && (same & lt) == 0) cursor[blk] = base + __popc(same);
+      __syncwarp();
+      if (valid) {
+        const long long dst = base + __popc(same & lt);
+        if (dst < capacity) {
+          ro[dst] = sp.bos + row0 + e / p.slots;
+          ho[dst] = hq;
+          so[dst] = e % p.slots;
+        }
       }
     }
   }
