@@ -232,15 +232,26 @@ merge_kernel(const TP* __restrict__ part_o, const float* __restrict__ part_lse,
   for (int e = 0; e < EPV; ++e) acc[e] = 0.f;
   float wsum = 0.f;
   const TP* po = part_o + r * slots * (size_t)d + c * EPV;
-  for (int i = 0; i < slots; ++i) {
-    const float li = ls[i];
-    if (!(li > -INFINITY)) continue;                         // unwritten: never touch its data
-    const float w = exp2f(li - mg);
-    wsum += w;
-    const uint4 raw = *reinterpret_cast<const uint4*>(po + (size_t)i * d);
-    const TP* vals = reinterpret_cast<const TP*>(&raw);
+  // One 16-byte load per thread at a time leaves the memory system short of requests, so
+  // the slots are taken eight at a time: all loads first, then the sums in slot order.
+  constexpr int kAhead = 8;
+  for (int i0 = 0; i0 < slots; i0 += kAhead) {
+    float li[kAhead];
+    uint4 raw[kAhead];
 #pragma unroll
-    for (int e = 0; e < EPV; ++e) acc[e] = fmaf(w, Elem<TP>::to_f(vals[e]), acc[e]);
+    for (int u = 0; u < kAhead; ++u) li[u] = (i0 + u < slots) ? ls[i0 + u] : -INFINITY;
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u)                           // unwritten: never touch its data
+      raw[u] = (li[u] > -INFINITY) ? *reinterpret_cast<const uint4*>(po + (size_t)(i0 + u) * d) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      if (!(li[u] > -INFINITY)) continue;
+      const float w = exp2f(li[u] - mg);
+      wsum += w;
+      const TP* vals = reinterpret_cast<const TP*>(&raw[u]);
+#pragma unroll
+      for (int e = 0; e < EPV; ++e) acc[e] = fmaf(w, Elem<TP>::to_f(vals[e]), acc[e]);
+    }
   }
   const float inv = 1.f / wsum;                              // wsum == 0 -> NaN, as the reference
   const size_t s = r % tokens, bh = r / tokens;

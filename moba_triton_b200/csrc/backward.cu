@@ -262,12 +262,23 @@ dq_reduce_kernel(const T* __restrict__ dq_part, const float* __restrict__ part_l
   for (int e = 0; e < EPV; ++e) acc[e] = 0.f;
   const float* ls = part_lse + r * slots;
   const T* src = dq_part + r * slots * (size_t)d + c * EPV;
-  for (int i = 0; i < slots; ++i) {
-    if (!(ls[i] > -INFINITY)) continue;
-    const uint4 raw = *reinterpret_cast<const uint4*>(src + (size_t)i * d);
-    const T* vals = reinterpret_cast<const T*>(&raw);
+  // eight slots at a time: all loads first (more requests in flight), then the sums in slot order
+  constexpr int kAhead = 8;
+  for (int i0 = 0; i0 < slots; i0 += kAhead) {
+    bool live[kAhead];
+    uint4 raw[kAhead];
 #pragma unroll
-    for (int e = 0; e < EPV; ++e) acc[e] += Elem<T>::to_f(vals[e]);
+    for (int u = 0; u < kAhead; ++u) live[u] = (i0 + u < slots) && (ls[i0 + u] > -INFINITY);
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u)
+      raw[u] = live[u] ? *reinterpret_cast<const uint4*>(src + (size_t)(i0 + u) * d) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      if (!live[u]) continue;
+      const T* vals = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+      for (int e = 0; e < EPV; ++e) acc[e] += Elem<T>::to_f(vals[e]);
+    }
   }
   const size_t s = r % tokens, bh = r / tokens;
   const size_t h = bh % q_heads, b = bh / q_heads;

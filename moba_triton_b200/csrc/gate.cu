@@ -48,11 +48,23 @@ pool_kernel(const T* __restrict__ k, const int32_t* __restrict__ cu, T* __restri
 #pragma unroll
   for (int e = 0; e < EPV; ++e) acc[e] = 0.0;
   if (rg < groups) {
-    for (int r = rg; r < hi - lo; r += groups) {
-      uint4 raw = *reinterpret_cast<const uint4*>(src + r * row_stride);
-      const T* vals = reinterpret_cast<const T*>(&raw);
+    // eight rows in flight per thread: the loads do not depend on one another
+    constexpr int kAhead = 8;
+    for (int r0 = rg; r0 < hi - lo; r0 += groups * kAhead) {
+      uint4 raw[kAhead];
 #pragma unroll
-      for (int e = 0; e < EPV; ++e) acc[e] += (double)Elem<T>::to_f(vals[e]);
+      for (int u = 0; u < kAhead; ++u) {
+        const int r = r0 + u * groups;
+        raw[u] = (r < hi - lo) ? *reinterpret_cast<const uint4*>(src + r * row_stride) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < kAhead; ++u) {
+        if (r0 + u * groups < hi - lo) {
+          const T* vals = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+          for (int e = 0; e < EPV; ++e) acc[e] += (double)Elem<T>::to_f(vals[e]);
+        }
+      }
     }
   }
   __shared__ double red[128 * EPV];

@@ -6,7 +6,7 @@
 //               histogram over blocks -> tile_counts[seq,kvh][block][g*C + chunk]
 //   2. colscan  one warp per (sequence, kv head, block): exclusive scan of that
 //               block's tile counts in (g, chunk) order; total -> col_nnz
-//   3. offsets  one CTA per (sequence, kv head): exclusive scan over blocks ->
+//   3. offsets  per (sequence, kv head): exclusive scan over blocks ->
 //               col_offsets, and the longest-first dispatch order (stable
 //               descending sort of col_nnz, by rank counting)
 //   4. scatter  one warp per (row chunk, sequence, query head): walks its rows in
@@ -112,7 +112,7 @@ colscan_kernel(const int32_t* __restrict__ cu, int32_t* __restrict__ tile_counts
   if (lane == 0) *out_nnz = running;
 }
 
-// One CTA per (sequence, kv head): col_offsets and the dispatch order.
+// (sequence, kv head) x (128 columns): col_offsets (first CTA of the row) and the dispatch order.
 __global__ void __launch_bounds__(1024)
 offsets_order_kernel(const int32_t* __restrict__ col_nnz, int32_t* __restrict__ col_offsets,
                      int32_t* __restrict__ order, int nb) {
@@ -149,22 +149,28 @@ offsets_order_kernel(const int32_t* __restrict__ col_nnz, int32_t* __restrict__ 
     }
     __syncthreads();
     const int carry = carry_s;
-    if (i < nb) off[i] = carry + warp_sums[warp] + incl - v;
+    if (i < nb && blockIdx.y == 0) off[i] = carry + warp_sums[warp] + incl - v;
     __syncthreads();
     if (threadIdx.x == 1023) carry_s = carry + warp_sums[warp] + incl;
     __syncthreads();
   }
-  if (threadIdx.x == 0) off[nb] = carry_s;
-  // stable descending rank: position of column i = #{j : n_j > n_i or (n_j == n_i and j < i)}
-  for (int i = threadIdx.x; i < nb; i += 1024) {
+  if (threadIdx.x == 0 && blockIdx.y == 0) off[nb] = carry_s;
+  // stable descending rank: position of column i = #{j : n_j > n_i or (n_j == n_i and j < i)}.
+  // nb^2 comparisons in all: CTA y of the row ranks columns [128 y, 128 y + 128), eight
+  // threads per column over interleaved j.
+  const int i = (int)blockIdx.y * 128 + (int)(threadIdx.x >> 3), part = threadIdx.x & 7;
+  int rank = 0;
+  if (i < nb) {
     const int ni = cnt[i];
-    int rank = 0;
-    for (int j = 0; j < nb; ++j) {
+    for (int j = part; j < nb; j += 8) {
       const int nj = cnt[j];
       rank += (nj > ni || (nj == ni && j < i)) ? 1 : 0;
     }
-    ord[rank] = i;
   }
+  rank += __shfl_xor_sync(0xffffffffu, rank, 1);
+  rank += __shfl_xor_sync(0xffffffffu, rank, 2);
+  rank += __shfl_xor_sync(0xffffffffu, rank, 4);
+  if (i < nb && part == 0) ord[rank] = i;
 }
 
 // One warp per (row chunk, sequence, query head); four chunks (warps) per CTA, each with its
@@ -278,7 +284,8 @@ int launch_transpose(const moba_b200_problem& p, const int32_t* block_idx, const
   colscan_kernel<<<grid_cols, 128, 0, st>>>(cu, tiles, col_nnz, p, g.chunk_rows, g.chunks);
   MOBA_LAUNCH_OK("colscan_kernel"); }
   { KernelTimer t__("offsets_order_kernel", st);
-  offsets_order_kernel<<<p.n_seq * p.kv_heads, 1024, hist_bytes, st>>>(col_nnz, col_offsets, order, p.num_blocks);
+  offsets_order_kernel<<<dim3(p.n_seq * p.kv_heads, (p.num_blocks + 127) / 128), 1024, hist_bytes, st>>>(
+      col_nnz, col_offsets, order, p.num_blocks);
   MOBA_LAUNCH_OK("offsets_order_kernel"); }
   { KernelTimer t__("scatter_kernel", st);
   dim3 grid_scatter((g.chunks + kScatterWarps - 1) / kScatterWarps, p.n_seq * p.q_heads);
