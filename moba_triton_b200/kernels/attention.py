@@ -38,15 +38,42 @@ class MoBAAttentionFunction(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None, None
 
 
+def _kv_head_passes(q, k, v, kv_heads_per_pass: int):
+    """Slices of (q, k, v) that hold whole groups of query heads with their KV heads."""
+    hkv = k.shape[2]
+    group = q.shape[2] // hkv
+    for h0 in range(0, hkv, kv_heads_per_pass):
+        h1 = min(hkv, h0 + kv_heads_per_pass)
+        yield q[:, :, h0 * group:h1 * group], k[:, :, h0:h1], v[:, :, h0:h1]
+
+
 def moba_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cfg: MoBAConfig,
                    index: Optional[CSCIndex] = None, causal: bool = True,
                    cu_seqlens: Optional[torch.Tensor] = None,
-                   max_seqlen: Optional[int] = None) -> torch.Tensor:
+                   max_seqlen: Optional[int] = None,
+                   kv_heads_per_pass: Optional[int] = None) -> torch.Tensor:
     """MoBA attention with gradient support.
 
     q [B,S,Hq,D]; k, v [B,S,Hkv,D] with Hkv dividing Hq (grouped-query heads map
     h -> h // (Hq/Hkv)); packed batches are [1,T,H,D] with `cu_seqlens` (int32,
     on the device) and `max_seqlen`. `index` holds routing fixed and carries its
     own packing metadata. `causal=False` removes only the mask inside the
-    query's own block. Returns [B,S,Hq,D] in the dtype of q."""
+    query's own block. Returns [B,S,Hq,D] in the dtype of q.
+
+    `kv_heads_per_pass` (not in the reference, which planned but never built a
+    host-side chunking of the op, docs/deferred-decisions.md:152-220) runs the op
+    over that many KV heads at a time, each with its group of query heads. KV
+    heads are independent, so the result is the same bit for bit, while the
+    per-(query, slot) partial outputs and dQ partials, which are `slots` times the
+    size of the output, exist for one pass only: at q [1,524288,32,128] with 8 KV
+    heads that is 4.3 GB per pass instead of 34 GB."""
+    if kv_heads_per_pass is not None:
+        if index is not None:
+            raise ValueError("kv_heads_per_pass cannot be combined with index (an index spans every head)")
+        if kv_heads_per_pass < 1:
+            raise ValueError(f"kv_heads_per_pass must be positive, got {kv_heads_per_pass}")
+        if kv_heads_per_pass < k.shape[2]:
+            outs = [MoBAAttentionFunction.apply(qs, ks, vs, cfg, None, causal, cu_seqlens, max_seqlen)
+                    for qs, ks, vs in _kv_head_passes(q, k, v, kv_heads_per_pass)]
+            return torch.cat(outs, dim=2)
     return MoBAAttentionFunction.apply(q, k, v, cfg, index, causal, cu_seqlens, max_seqlen)

@@ -136,9 +136,40 @@ def combine_partials(part_m, part_l, part_acc, out_dtype: torch.dtype, block_m=N
 
 
 def moba_forward(q, k, v, cfg: MoBAConfig, index: Optional[CSCIndex] = None, causal: bool = True,
-                 partials_dtype: Optional[torch.dtype] = None, cu_seqlens=None, max_seqlen=None):
+                 partials_dtype: Optional[torch.dtype] = None, cu_seqlens=None, max_seqlen=None,
+                 kv_heads_per_pass: Optional[int] = None):
     """MoBA attention output [B,S,H,D] in the dtype of q (inference path; no
-    log-sum-exp kept). Reference: moba_fwd.py:783-835."""
+    log-sum-exp kept). Reference: moba_fwd.py:783-835.
+
+    `kv_heads_per_pass` (not in the reference) runs that many KV heads at a time,
+    each with its group of query heads, into one set of partial buffers that every
+    pass reuses: same result bit for bit, partial-output memory of one pass."""
+    if kv_heads_per_pass is not None:
+        if index is not None:
+            raise ValueError("kv_heads_per_pass cannot be combined with index (an index spans every head)")
+        if kv_heads_per_pass < 1:
+            raise ValueError(f"kv_heads_per_pass must be positive, got {kv_heads_per_pass}")
+        hkv = k.shape[2]
+        if kv_heads_per_pass < hkv:
+            group = q.shape[2] // hkv
+            out = torch.empty_like(q)
+            partials = None
+            for h0 in range(0, hkv, kv_heads_per_pass):
+                h1 = min(hkv, h0 + kv_heads_per_pass)
+                qs = q[:, :, h0 * group:h1 * group].contiguous()
+                ks, vs = k[:, :, h0:h1].contiguous(), v[:, :, h0:h1].contiguous()
+                _validate(qs, ks, vs, cfg, cu_seqlens, max_seqlen)
+                _lib.require_cuda(qs, ks, vs, cu_seqlens)
+                idx = build_csc_fused(qs, ks, cfg, cu_seqlens=cu_seqlens, max_seqlen=max_seqlen)
+                if partials is not None and partials[1].shape[1] != qs.shape[2]:
+                    partials = None                          # the last pass may hold fewer heads
+                if partials is None:
+                    partials = empty_partials(qs.shape, idx.max_slots, qs.device,
+                                              partials_dtype if partials_dtype is not None else q.dtype)
+                part_lse, part_o = attend_partials(qs, ks, vs, cfg, idx, causal=causal,
+                                                   partials_dtype=partials_dtype, partials=partials)
+                out[:, :, h0 * group:h1 * group] = merge_partials(part_lse, part_o, q.dtype)
+            return out
     if index is not None:
         cu_seqlens, max_seqlen = index.cu_seqlens, index.max_seqlen
     _validate(q, k, v, cfg, cu_seqlens, max_seqlen)

@@ -303,6 +303,27 @@ def test_unselected_blocks_get_exact_zero_gradients(device, kernel_path):
         assert not dv[0, blk * 64:(blk + 1) * 64, h].any()
 
 
+def test_kv_heads_per_pass_is_bitwise_the_whole_op(device, kernel_path):
+    """Running the op a few KV heads at a time (host-side chunking that bounds the partial
+    buffers) gives the same bits as one call: KV heads are independent."""
+    cfg = moba.MoBAConfig(block_size=128, top_k=4, dtype=torch.bfloat16)
+    q, k, v, do = make_qkv((1, 1024, 12, 64), 3, dtype=torch.bfloat16, seed=23, with_do=True)
+    qd, kd, vd, dod = _dev(q, k, v, do, device=device)
+
+    def run(**kw):
+        qq, kk, vv = (t.clone().requires_grad_(True) for t in (qd, kd, vd))
+        out = moba.moba_attention(qq, kk, vv, cfg, **kw)
+        out.backward(dod)
+        return out.detach(), qq.grad, kk.grad, vv.grad
+
+    whole = run()
+    for per_pass in (1, 2):                                  # 2: the last pass holds one head
+        for got, want in zip(run(kv_heads_per_pass=per_pass), whole):
+            assert torch.equal(got, want)
+        assert torch.equal(moba.moba_forward(qd, kd, vd, cfg, kv_heads_per_pass=per_pass), whole[0])
+    assert torch.equal(moba.moba_forward(qd, kd, vd, cfg, kv_heads_per_pass=8), whole[0])
+
+
 def test_gqa_equals_expanded_kv(device, kernel_path):
     cfg = moba.MoBAConfig(64, 4)
     q, k, v, do = make_qkv((1, 1024, 8, 64), 2, dtype=torch.bfloat16, seed=6, with_do=True)

@@ -128,3 +128,14 @@ def test_backend_adapter_follows_the_reference_protocol_and_never_raises():
     assert isinstance(ok, bool) and isinstance(reason, str)
     if not torch.cuda.is_available():
         assert not ok and reason                       # says why instead of raising
+
+
+def test_kv_heads_per_pass_arguments_are_checked_before_any_device_work():
+    q = torch.zeros(1, 256, 4, 64, dtype=torch.bfloat16)
+    k = v = torch.zeros(1, 256, 2, 64, dtype=torch.bfloat16)
+    cfg = moba.MoBAConfig(block_size=128, top_k=2, dtype=torch.bfloat16)
+    for fn in (moba.moba_attention, moba.moba_forward):
+        with pytest.raises(ValueError, match="kv_heads_per_pass must be positive"):
+            fn(q, k, v, cfg, kv_heads_per_pass=0)
+        with pytest.raises(ValueError, match="cannot be combined with index"):
+            fn(q, k, v, cfg, index=object(), kv_heads_per_pass=1)
