@@ -344,20 +344,51 @@ def run_ours(args, wl, rank, world, local_rank):
             fwd()
         ms_fwd = timed(fwd, max(2, args.steps // 2)) / max(2, args.steps // 2)
 
-    # end to end: host buffers in, host buffers out, through the public API
+    # end to end: host buffers in, host buffers out, through the public API. Every step copies
+    # its q, k, v, dO from pinned host memory and its O, dQ, dK, dV back. The copies run on two
+    # streams of their own, ordered against the op by events: dO goes up while the forward runs,
+    # O comes down while the backward runs, and a step's uploads start while the previous
+    # step's gradients are still on their way down (PCIe carries both directions at once).
     outs_host = [torch.empty_like(h).pin_memory() for h in (host[0], host[0], host[1], host[2])]
+    main_s = torch.cuda.current_stream()
+    h2d_s, d2h_s = torch.cuda.Stream(), torch.cuda.Stream()
 
     def e2e_step():
-        qd, kd, vd, dod = (h.to(dev, non_blocking=True) for h in host)
+        with torch.cuda.stream(h2d_s):
+            qd, kd, vd = (h.to(dev, non_blocking=True) for h in host[:3])
+            ev_qkv = h2d_s.record_event()
+            dod = host[3].to(dev, non_blocking=True)
+            ev_do = h2d_s.record_event()
+        for t in (qd, kd, vd, dod):
+            t.record_stream(main_s)                          # allocated on the copy stream, used here
+        main_s.wait_event(ev_qkv)
         qd.requires_grad_(True); kd.requires_grad_(True); vd.requires_grad_(True)
         out = moba.moba_attention(qd, kd, vd, cfg, **kw)
+        ev_fwd = main_s.record_event()
+        main_s.wait_event(ev_do)
         out.backward(dod)
-        for dst, src in zip(outs_host, (out.detach(), qd.grad, kd.grad, vd.grad)):
-            dst.copy_(src, non_blocking=True)
+        ev_bwd = main_s.record_event()
+        results = (out.detach(), qd.grad, kd.grad, vd.grad)
+        with torch.cuda.stream(d2h_s):
+            d2h_s.wait_event(ev_fwd)
+            outs_host[0].copy_(results[0], non_blocking=True)
+            d2h_s.wait_event(ev_bwd)
+            for dst, src in zip(outs_host[1:], results[1:]):
+                dst.copy_(src, non_blocking=True)
+        for t in results:
+            t.record_stream(d2h_s)
+
+    def e2e_run(n):                                          # the timed region ends when the last copy has landed
+        for _ in range(n):
+            e2e_step()
+        main_s.wait_stream(d2h_s)
 
     e2e_steps = max(2, min(args.steps, 5))
-    e2e_step()
-    ms_e2e = timed(e2e_step, e2e_steps) / e2e_steps
+    e2e_run(1)
+    ms_e2e = timed(lambda: e2e_run(e2e_steps), 1) / e2e_steps
+    # the overlapped path must deliver what the plain call computes (the op is deterministic)
+    e2e_ok = bool(torch.equal(outs_host[0], step().detach().cpu()) and
+                  torch.equal(outs_host[1], q.grad.cpu()))
     h2d = sum(h.numel() * h.element_size() for h in host)
     d2h = sum(h.numel() * h.element_size() for h in outs_host)
 
@@ -409,7 +440,7 @@ def run_ours(args, wl, rank, world, local_rank):
             "fwd_ms": ms_fwd, "fwd_tflops": acct["f_fwd"] / (ms_fwd * 1e-3) / 1e12,
             "op_roofline": {"t_roof_ms": t_roof * 1e3, "frac": t_roof * 1e3 / ms_step,
                             "peak": f"{pk['tensor_burst']} TFLOP/s burst, {pk['hbm']} GB/s ({pk['source']})"},
-            "e2e": {"value": total_f / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+            "e2e": {"value": total_f / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e, "outputs_match_resident_run": e2e_ok,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches,
             "clocks": clock_info,
