@@ -133,7 +133,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_kv_rows = p.n_seq * p.kv_heads;
 #ifdef MOBA_WAIT_STATS
-  const WaitCtx wc{&bars->abort, error_word, nullptr};
+  __shared__ unsigned long long wait_stats[32];
+  if (threadIdx.x < 32) wait_stats[threadIdx.x] = 0;
+  const long long kernel_t0 = clock64();
+  const WaitCtx wc{&bars->abort, error_word, wait_stats};
 #else
   const WaitCtx wc{&bars->abort, error_word};
 #endif
@@ -185,7 +188,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       for (int i = 0; i < nt; ++i, ++t) {
         // The stage's metadata was written before the gather warps published the stage, the
         // MMA warp waited for that before issuing S / dP, and sp_full follows those MMAs.
-        mbar_wait(&bars->sp_full, t & 1, wc);
+        mbar_wait(&bars->sp_full, t & 1, wc, 1);
         const int4 mt = bars->meta[t % NST][r];
         const int row = mt.x < 0 ? 0 : mt.x, head = mt.y >> 8, slot = mt.y & 0xff;
         const bool live = mt.x >= 0;
@@ -229,7 +232,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         mbar_arrive(&bars->pds_full);
 
         // ---- dQ rows of this tile: this warpgroup stores columns [wg D/2, (wg+1) D/2) ----
-        mbar_wait(&bars->dq_full, t & 1, wc);
+        mbar_wait(&bars->dq_full, t & 1, wc, 2);
         tc_fence_after();
         // Stage the 16-bit dQ tile in the P buffer (the MMAs that read it have retired) so
         // that eight or sixteen adjacent lanes write each row; one row per thread straight to
@@ -270,7 +273,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         asm volatile("bar.sync 2, 256;" ::: "memory");   // the staging area is P again
       }
       // ---- the column's dV (warpgroup 0) and dK (warpgroup 1), one key row per thread ----
-      mbar_wait(&bars->acc_full, it_cnt & 1, wc);
+      mbar_wait(&bars->acc_full, it_cnt & 1, wc, 3);
       tc_fence_after();
       {
         unsigned char* dst = reinterpret_cast<unsigned char*>(
@@ -308,15 +311,15 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         const bool partial = c.keys < kTile;
         const uint32_t kb = it_cnt % NKV, ku = it_cnt / NKV;
         const uint32_t aK = smem_u32(sK) + kb * Cfg::kOperand, aV = smem_u32(sV) + kb * Cfg::kOperand;
-        mbar_wait(&bars->k_full[kb], ku & 1, wc);
-        mbar_wait(&bars->v_full[kb], ku & 1, wc);
-        if (partial) { mbar_wait(&bars->k_fix, pt_cnt & 1, wc); mbar_wait(&bars->v_fix, pt_cnt & 1, wc); }
-        if (it_cnt >= 1) mbar_wait(&bars->acc_read, (it_cnt - 1) & 1, wc);   // dK/dV columns free
+        mbar_wait(&bars->k_full[kb], ku & 1, wc, 4);
+        mbar_wait(&bars->v_full[kb], ku & 1, wc, 5);
+        if (partial) { mbar_wait(&bars->k_fix, pt_cnt & 1, wc, 6); mbar_wait(&bars->v_fix, pt_cnt & 1, wc, 6); }
+        if (it_cnt >= 1) mbar_wait(&bars->acc_read, (it_cnt - 1) & 1, wc, 7);   // dK/dV columns free
         for (int i = 0; i < nt; ++i, ++t) {
           const uint32_t st = t % NST, us = t / NST;
           const uint32_t aQ = smem_u32(sQ) + st * Cfg::kOperand, aG = smem_u32(sG) + st * Cfg::kOperand;
-          mbar_wait(&bars->qd_full[st], us & 1, wc);
-          if (t >= 1) mbar_wait(&bars->dq_read, (t - 1) & 1, wc);            // S/dQ columns, P/dS smem free
+          mbar_wait(&bars->qd_full[st], us & 1, wc, 8);
+          if (t >= 1) mbar_wait(&bars->dq_read, (t - 1) & 1, wc, 9);            // S/dQ columns, P/dS smem free
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < D / 16; ++ks) {
@@ -330,7 +333,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
           }
           if (leader) umma_commit(&bars->sp_full);
 
-          mbar_wait(&bars->pds_full, t & 1, wc);
+          mbar_wait(&bars->pds_full, t & 1, wc, 10);
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {            // 16 queries per step
@@ -373,7 +376,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         const int kvh = c.kv_row % p.kv_heads;
         const int tok0 = (int)(c.b * p.tokens) + c.key0;
         const uint32_t kb = it_cnt % NKV, ku = it_cnt / NKV;
-        if (ku >= 1) mbar_wait(&bars->kv_free[kb], (ku - 1) & 1, wc);
+        if (ku >= 1) mbar_wait(&bars->kv_free[kb], (ku - 1) & 1, wc, 11);
         mbar_expect_tx(&bars->k_full[kb], Cfg::kOperand);
         for (int s = 0; s < Cfg::kSubs; ++s)
           tma_load_3d(sK + kb * Cfg::kOperand + s * kSub, &k_map, &bars->k_full[kb], s * 64, kvh, tok0);
@@ -395,7 +398,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
     const int pt = threadIdx.x - kGatherWarp0 * 32;
     constexpr int CPR = D / 8, RPP = 128 / CPR;
     uint32_t t = 0, it_cnt = 0;
-    int pending[2] = {-1, -1};                            // stages in flight, oldest first
     for (int round = 0; round * (int)gridDim.x < n_items; ++round) {
       const int item = snake_item(round);
       if (item >= n_items) continue;
@@ -404,23 +406,15 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       const int nt = (c.n + kTile - 1) / kTile;
       const uint32_t kb = it_cnt % NKV, ku = it_cnt / NKV;
       if (c.keys < kTile) {
-        // Publish the previous column's last tile first: the K/V load awaited below may
-        // be issued only after that tile's MMAs have run.
-        if (NST > 1 && pending[0] >= 0) {
-          cp_async_wait<0>();
-          fence_proxy_async();
-          mbar_arrive(&bars->qd_full[pending[0]]);
-          pending[0] = -1;
-        }
         const int dead = kTile - c.keys;
-        mbar_wait(&bars->k_full[kb], ku & 1, wc);
+        mbar_wait(&bars->k_full[kb], ku & 1, wc, 12);
         for (int i = pt; i < dead * 8 * Cfg::kSubs; i += 128) {
           const int s = i / (dead * 8), rr = c.keys + (i % (dead * 8)) / 8, ch = i % 8;
           *reinterpret_cast<uint4*>(sK + kb * Cfg::kOperand + s * kSub + rr * 128 + ch * 16) = make_uint4(0, 0, 0, 0);
         }
         fence_proxy_async();
         mbar_arrive(&bars->k_fix);
-        mbar_wait(&bars->v_full[kb], ku & 1, wc);
+        mbar_wait(&bars->v_full[kb], ku & 1, wc, 12);
         for (int i = pt; i < dead * 8 * Cfg::kSubs; i += 128) {
           const int s = i / (dead * 8), rr = c.keys + (i % (dead * 8)) / 8, ch = i % 8;
           *reinterpret_cast<uint4*>(sV + kb * Cfg::kOperand + s * kSub + rr * 128 + ch * 16) = make_uint4(0, 0, 0, 0);
@@ -444,7 +438,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
           mt = make_int4(n_row, (n_head << 8) | n_slot, __float_as_int(lse[qr]), __float_as_int(delta[qr]));
         }
         if (e + kTile < c.n) { n_row = rows_i[e + kTile]; n_head = heads_i[e + kTile]; n_slot = slots_i[e + kTile]; }
-        if (us >= 1) mbar_wait(&bars->qd_empty[st], (us - 1) & 1, wc);
+        if (us >= 1) mbar_wait(&bars->qd_empty[st], (us - 1) & 1, wc, 13);
         bars->meta[st][pt] = mt;
         bars->row_off[pt] = off;
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -462,31 +456,25 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         }
         cp_async_commit();
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (NST == 1) {
-          cp_async_wait<0>();
-          fence_proxy_async();
-          mbar_arrive(&bars->qd_full[st]);
-        } else {
-          if (pending[0] >= 0) {
-            cp_async_wait<1>();
-            fence_proxy_async();
-            mbar_arrive(&bars->qd_full[pending[0]]);
-          }
-          pending[0] = (int)st;
-        }
+        // Published as soon as it has landed: these warps have nothing else to do until the
+        // next stage frees, and a tile held back until then costs the MMA warp a wait.
+        cp_async_wait<0>();
+        fence_proxy_async();
+        mbar_arrive(&bars->qd_full[st]);
       }
       ++it_cnt;
-    }
-    if (NST > 1 && pending[0] >= 0) {
-      cp_async_wait<0>();
-      fence_proxy_async();
-      mbar_arrive(&bars->qd_full[pending[0]]);
     }
   }
 
   tc_fence_before();
   __syncthreads();
   if (warp == kMmaWarp) tmem_dealloc(tmem, 512);
+#ifdef MOBA_WAIT_STATS
+  if (threadIdx.x < 32) {
+    unsigned long long* out = reinterpret_cast<unsigned long long*>(error_word + 64) + (size_t)blockIdx.x * 32;
+    out[threadIdx.x] = threadIdx.x == 31 ? (unsigned long long)(clock64() - kernel_t0) : wait_stats[threadIdx.x];
+  }
+#endif
 }
 
 template <int D, typename T>
