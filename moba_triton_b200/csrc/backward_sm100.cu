@@ -314,7 +314,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         mbar_wait(&bars->k_full[kb], ku & 1, wc, 4);
         mbar_wait(&bars->v_full[kb], ku & 1, wc, 5);
         if (partial) { mbar_wait(&bars->k_fix, pt_cnt & 1, wc, 6); mbar_wait(&bars->v_fix, pt_cnt & 1, wc, 6); }
-        if (it_cnt >= 1) mbar_wait(&bars->acc_read, (it_cnt - 1) & 1, wc, 7);   // dK/dV columns free
         for (int i = 0; i < nt; ++i, ++t) {
           const uint32_t st = t % NST, us = t / NST;
           const uint32_t aQ = smem_u32(sQ) + st * Cfg::kOperand, aG = smem_u32(sG) + st * Cfg::kOperand;
@@ -334,6 +333,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
           if (leader) umma_commit(&bars->sp_full);
 
           mbar_wait(&bars->pds_full, t & 1, wc, 10);
+          // the previous column's dK / dV have been read out (S and dP of this tile did not need that)
+          if (i == 0 && it_cnt >= 1) mbar_wait(&bars->acc_read, (it_cnt - 1) & 1, wc, 7);
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {            // 16 queries per step
@@ -341,16 +342,18 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
                      id_acc, (i > 0 || ks > 0));
           }
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            if (leader) umma_f16(tmem + cDK, make_sdesc(aS + ks * 2048, kSub, 1024), make_sdesc(aQ + ks * 2048, kSub, 1024),
-                     id_acc, (i > 0 || ks > 0));
-          }
-#pragma unroll
           for (int ks = 0; ks < 8; ++ks) {            // 16 keys per step
             if (leader) umma_f16(tmem + cDQ, make_sdesc(aS + (ks >> 2) * kSub + (ks & 3) * 32, 16, 1024),
                      make_sdesc(aK + ks * 2048, kSub, 1024), id_dq, ks > 0);
           }
+          // dQ is what the elementwise warps wait for, and they stage it in the P buffer, which
+          // dV has finished reading by then; dK runs while they write dQ out.
           if (leader) umma_commit(&bars->dq_full);
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            if (leader) umma_f16(tmem + cDK, make_sdesc(aS + ks * 2048, kSub, 1024), make_sdesc(aQ + ks * 2048, kSub, 1024),
+                     id_acc, (i > 0 || ks > 0));
+          }
           if (leader) umma_commit(&bars->qd_empty[st]);
           if (i == nt - 1) { if (leader) umma_commit(&bars->acc_full); if (leader) umma_commit(&bars->kv_free[kb]); }
         }
