@@ -35,7 +35,12 @@ template <int D> struct BwdCfg {
   static constexpr int kStages = (D == 64) ? 2 : 1;      // Q / dO gather stages
   static constexpr int kKvBufs = (D == 64) ? 2 : 1;
   static constexpr int kPBytes = 2 * kSub;
-  static constexpr int kSmemData = 2 * kKvBufs * kOperand + 2 * kStages * kOperand + 2 * kPBytes;
+  // At head_dim 64 there is room for a staging tile of dQ of its own, so dQ can be the first
+  // of a tile's last three MMAs and be written out while dV and dK run; at 128 it is staged
+  // in the P buffer, after dV has read that.
+  static constexpr bool kOwnStage = (D == 64);
+  static constexpr int kStageBytes = kOwnStage ? kSub * (D / 64) : 0;
+  static constexpr int kSmemData = 2 * kKvBufs * kOperand + 2 * kStages * kOperand + 2 * kPBytes + kStageBytes;
   static constexpr int kSmem = kSmemData + 1024 + 8192;
 };
 
@@ -128,7 +133,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
   unsigned char* sG = sQ + NST * Cfg::kOperand;              // dO, NST stages
   unsigned char* sP = sG + NST * Cfg::kOperand;
   unsigned char* sS = sP + Cfg::kPBytes;                     // dS
-  Bars* bars = reinterpret_cast<Bars*>(sS + Cfg::kPBytes);
+  unsigned char* sO = Cfg::kOwnStage ? sS + Cfg::kPBytes : sP;   // staging of the 16-bit dQ tile
+  Bars* bars = reinterpret_cast<Bars*>(sS + Cfg::kPBytes + Cfg::kStageBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_kv_rows = p.n_seq * p.kv_heads;
@@ -234,9 +240,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         // ---- dQ rows of this tile: this warpgroup stores columns [wg D/2, (wg+1) D/2) ----
         mbar_wait(&bars->dq_full, t & 1, wc, 2);
         tc_fence_after();
-        // Stage the 16-bit dQ tile in the P buffer (the MMAs that read it have retired) so
-        // that eight or sixteen adjacent lanes write each row; one row per thread straight to
-        // global memory would touch 32 lines per instruction.
+        // Stage the 16-bit dQ tile in shared memory (a tile of its own, or the P buffer once
+        // dV has read it) so that eight or sixteen adjacent lanes write each row; one row per
+        // thread straight to global memory would touch 32 lines per instruction.
 #pragma unroll 1
         for (int ch = 0; ch < D / 64; ++ch) {
           tmem_ld32(tmem + lane_off + cDQ + wg * (D / 2) + ch * 32, sv);
@@ -249,7 +255,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
             w.y = pack2<T>(__uint_as_float(sv[g * 8 + 2]) * softmax_scale, __uint_as_float(sv[g * 8 + 3]) * softmax_scale);
             w.z = pack2<T>(__uint_as_float(sv[g * 8 + 4]) * softmax_scale, __uint_as_float(sv[g * 8 + 5]) * softmax_scale);
             w.w = pack2<T>(__uint_as_float(sv[g * 8 + 6]) * softmax_scale, __uint_as_float(sv[g * 8 + 7]) * softmax_scale);
-            *reinterpret_cast<uint4*>(sP + ((c16 + g) >> 3) * kSub + swz128(r, (c16 + g) & 7)) = w;
+            *reinterpret_cast<uint4*>(sO + ((c16 + g) >> 3) * kSub + swz128(r, (c16 + g) & 7)) = w;
           }
         }
         tc_fence_before();
@@ -266,11 +272,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
           for (int pass = 0; pass < kTile / RPPO; ++pass) {
             const int rr = pass * RPPO + tid / CPRO;
             unsigned char* op = bars->out_ptr[rr];
-            const uint4 w = *reinterpret_cast<const uint4*>(sP + (cc >> 3) * kSub + swz128(rr, cc & 7));
+            const uint4 w = *reinterpret_cast<const uint4*>(sO + (cc >> 3) * kSub + swz128(rr, cc & 7));
             if (op != nullptr) *reinterpret_cast<uint4*>(op + cc * 16) = w;
           }
         }
-        asm volatile("bar.sync 2, 256;" ::: "memory");   // the staging area is P again
+        asm volatile("bar.sync 2, 256;" ::: "memory");   // the staging tile may be written again
       }
       // ---- the column's dV (warpgroup 0) and dK (warpgroup 1), one key row per thread ----
       mbar_wait(&bars->acc_full, it_cnt & 1, wc, 3);
@@ -336,19 +342,24 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
           // the previous column's dK / dV have been read out (S and dP of this tile did not need that)
           if (i == 0 && it_cnt >= 1) mbar_wait(&bars->acc_read, (it_cnt - 1) & 1, wc, 7);
           tc_fence_after();
+          auto issue_dv = [&]() {
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {            // 16 queries per step
-            if (leader) umma_f16(tmem + cDV, make_sdesc(aP + ks * 2048, kSub, 1024), make_sdesc(aG + ks * 2048, kSub, 1024),
-                     id_acc, (i > 0 || ks > 0));
-          }
+            for (int ks = 0; ks < 8; ++ks) {          // 16 queries per step
+              if (leader) umma_f16(tmem + cDV, make_sdesc(aP + ks * 2048, kSub, 1024), make_sdesc(aG + ks * 2048, kSub, 1024),
+                       id_acc, (i > 0 || ks > 0));
+            }
+          };
+          // dQ is what the elementwise warps wait for: first if it has a staging tile of its
+          // own, else right after dV, whose operand P the staging overwrites. dK (and dV) run
+          // while they write dQ out.
+          if (!Cfg::kOwnStage) issue_dv();
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {            // 16 keys per step
             if (leader) umma_f16(tmem + cDQ, make_sdesc(aS + (ks >> 2) * kSub + (ks & 3) * 32, 16, 1024),
                      make_sdesc(aK + ks * 2048, kSub, 1024), id_dq, ks > 0);
           }
-          // dQ is what the elementwise warps wait for, and they stage it in the P buffer, which
-          // dV has finished reading by then; dK runs while they write dQ out.
           if (leader) umma_commit(&bars->dq_full);
+          if (Cfg::kOwnStage) issue_dv();
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             if (leader) umma_f16(tmem + cDK, make_sdesc(aS + ks * 2048, kSub, 1024), make_sdesc(aQ + ks * 2048, kSub, 1024),
