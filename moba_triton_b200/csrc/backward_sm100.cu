@@ -165,7 +165,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
-  constexpr uint32_t cS = 0, cDP = 128, cDV = 256, cDK = 256 + D, cDQ = 0;
+  // At head_dim 64 TMEM has room for dQ columns of their own; at 128 dQ lands on S.
+  constexpr uint32_t cS = 0, cDP = 128, cDV = 256, cDK = 256 + D, cDQ = Cfg::kOwnStage ? 256 + 2 * D : 0;
 
   const float softmax_scale = rsqrtf((float)D);
   const float cs = softmax_scale * kLog2e;
@@ -324,7 +325,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
           const uint32_t st = t % NST, us = t / NST;
           const uint32_t aQ = smem_u32(sQ) + st * Cfg::kOperand, aG = smem_u32(sG) + st * Cfg::kOperand;
           mbar_wait(&bars->qd_full[st], us & 1, wc, 8);
-          if (t >= 1) mbar_wait(&bars->dq_read, (t - 1) & 1, wc, 9);            // S/dQ columns, P/dS smem free
+          // Where dQ shares the S columns and its staging the P tile, S of this tile waits for
+          // the previous dQ to be read out. With columns and a staging tile of its own, S and
+          // dP run while the elementwise warps write dQ out: they finished reading S and dP
+          // before pds_full, and sp_full also covers the dV / dK that read P and dS.
+          if (!Cfg::kOwnStage && t >= 1) mbar_wait(&bars->dq_read, (t - 1) & 1, wc, 9);
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < D / 16; ++ks) {
