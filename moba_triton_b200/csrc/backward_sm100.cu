@@ -206,8 +206,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
 
         tc_fence_after();
         uint32_t sv[32], pv[32];
-#pragma unroll 1
-        for (int hc = 0; hc < 2; ++hc) {
+        // Away from the diagonal block and the ragged ends every lane keeps all 128 keys;
+        // such a tile runs without the per-element comparison.
+        const bool all_open = __all_sync(0xffffffffu, jmax >= kTile - 1);
+        auto p_ds_half = [&](int hc, auto masked) {
           const int col0 = wg * 64 + hc * 32;
           tmem_ld32(tmem + lane_off + cS + col0, sv);
           tmem_ld32(tmem + lane_off + cDP + col0, pv);
@@ -219,9 +221,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
             float pe[8], ds[8];
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
-              const int j = col0 + g * 8 + k;
               const float x = ex2(fmaf(__uint_as_float(sv[g * 8 + k]), cs, -lse_r));
-              pe[k] = (j <= jmax) ? x : 0.f;
+              if constexpr (decltype(masked)::value) pe[k] = (col0 + g * 8 + k <= jmax) ? x : 0.f;
+              else pe[k] = x;
               ds[k] = pe[k] * (__uint_as_float(pv[g * 8 + k]) - delta_r);
             }
             uint4 wp, wd;
@@ -233,6 +235,13 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
             *reinterpret_cast<uint4*>(p_sub + off) = wp;
             *reinterpret_cast<uint4*>(s_sub + off) = wd;
           }
+        };
+        if (all_open) {
+#pragma unroll 1
+          for (int hc = 0; hc < 2; ++hc) p_ds_half(hc, std::false_type{});
+        } else {
+#pragma unroll 1
+          for (int hc = 0; hc < 2; ++hc) p_ds_half(hc, std::true_type{});
         }
         fence_proxy_async();
         tc_fence_before();
