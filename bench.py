@@ -423,7 +423,7 @@ def run_ours(args, wl, rank, world, local_rank):
         # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised in
         # profiles/tensor_kernels_cfg2_ncu_full.md: measured at 2 082 816 (query head, block) pairs
         # and scaled by this run's pair count (the traffic is per-pair partial rows).
-        per_pair = {"bwd_sm100_kernel": (296.4e6 + 287.9e6) / 2082816, "fwd_sm100_kernel": (172.7e6 + 234.6e6) / 2082816,
+        per_pair = {"bwd_sm100_kernel": (297.1e6 + 287.1e6) / 2082816, "fwd_sm100_kernel": (172.7e6 + 234.6e6) / 2082816,
                     "gate_sm100_kernel": 33.8e6 / 2082816}
         traffic = per_pair[top] * acct["pairs"] if top in per_pair else None
         t_roof = max(acct["f_step"] / (pk["tensor_burst"] * 1e12), acct["bytes_step"] / (pk["hbm"] * 1e9))
