@@ -89,11 +89,21 @@ def check(rc: int, what: str) -> None:
     raise RuntimeError(f"{what}: {msg}")
 
 
+def call(name: str, device, what: str, *args) -> None:
+    """Runs entry point `name` with `device` made current for the call (the library
+    launches on the calling thread's current device) and that device's current
+    stream appended as the last argument; raises on a failure status."""
+    with torch.cuda.device(device):
+        check(getattr(load(), name)(*args, stream_ptr(device)), what)
+
+
 def device_status(device=None) -> int:
-    """Synchronises the current stream and returns (and clears) the device error
-    word: 0 when every tensor-core kernel ran to completion."""
+    """Synchronises the current stream of `device` (default: the current device) and
+    returns (and clears) its error word: 0 when every tensor-core kernel ran to
+    completion."""
     word = ctypes.c_uint(0)
-    check(load().moba_b200_device_status(ctypes.byref(word), stream_ptr(device)), "device_status")
+    with torch.cuda.device(device):
+        check(load().moba_b200_device_status(ctypes.byref(word), stream_ptr(device)), "device_status")
     return int(word.value)
 
 

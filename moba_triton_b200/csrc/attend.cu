@@ -189,6 +189,10 @@ int launch_fwd_portable(const moba_b200_problem& p, const void* q, const void* k
               p.block_size, p.head_dim, smem);
     return MOBA_B200_EUNSUPPORTED;
   }
+  if ((long long)p.n_seq * p.kv_heads > 65535) {
+    set_error("portable forward: %d sequences x %d heads exceed 65535 grid rows", p.n_seq, p.kv_heads);
+    return MOBA_B200_EUNSUPPORTED;
+  }
   dim3 grid(p.num_blocks, p.n_seq * p.kv_heads);
 #define MOBA_FWD(T, TP)                                                                        \
   do {                                                                                         \

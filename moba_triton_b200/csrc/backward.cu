@@ -227,6 +227,10 @@ int launch_bwd_portable(const moba_b200_problem& p, const void* q, const void* k
               "shared memory; unsupported", p.block_size, p.head_dim, dtype_size(p.dtype), smem);
     return MOBA_B200_EUNSUPPORTED;
   }
+  if ((long long)p.n_seq * p.kv_heads > 65535) {
+    set_error("portable backward: %d sequences x %d heads exceed 65535 grid rows", p.n_seq, p.kv_heads);
+    return MOBA_B200_EUNSUPPORTED;
+  }
   dim3 grid(p.num_blocks, p.n_seq * p.kv_heads);
 #define MOBA_BWD(T)                                                                            \
   do {                                                                                         \

@@ -195,8 +195,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       for (int i = 0; i < nt; ++i, ++t) {
         // The stage's metadata was written before the gather warps published the stage, the
         // MMA warp waited for that before issuing S / dP, and sp_full follows those MMAs.
-        mbar_wait(&bars->sp_full, t & 1, wc, 1);
-        const int4 mt = bars->meta[t % NST][r];
+        // A wait that gave up leaves the stage's metadata stale or never written: the row then
+        // counts as dead, so that no address is ever built from it.
+        const bool sp_ok = mbar_wait(&bars->sp_full, t & 1, wc, 1);
+        const int4 mt = sp_ok ? bars->meta[t % NST][r] : make_int4(-1, 0, 0, 0);
         const int row = mt.x < 0 ? 0 : mt.x, head = mt.y >> 8, slot = mt.y & 0xff;
         const bool live = mt.x >= 0;
         const float lse_r = __int_as_float(mt.z), delta_r = __int_as_float(mt.w);
@@ -248,7 +250,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         mbar_arrive(&bars->pds_full);
 
         // ---- dQ rows of this tile: this warpgroup stores columns [wg D/2, (wg+1) D/2) ----
-        mbar_wait(&bars->dq_full, t & 1, wc, 2);
+        const bool dq_ok = mbar_wait(&bars->dq_full, t & 1, wc, 2);
         tc_fence_after();
         // Stage the 16-bit dQ tile in shared memory (a tile of its own, or the P buffer once
         // dV has read it) so that eight or sixteen adjacent lanes write each row; one row per
@@ -270,7 +272,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         }
         tc_fence_before();
         mbar_arrive(&bars->dq_read);                     // S / dQ columns may be overwritten
-        if (wg == 0) bars->out_ptr[r] = live ? reinterpret_cast<unsigned char*>(
+        if (wg == 0) bars->out_ptr[r] = (live && dq_ok) ? reinterpret_cast<unsigned char*>(
                                                    dq_part + ((qrow * p.slots) + slot) * (size_t)D) : nullptr;
         asm volatile("bar.sync 2, 256;" ::: "memory");
         {
@@ -289,7 +291,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         asm volatile("bar.sync 2, 256;" ::: "memory");   // the staging tile may be written again
       }
       // ---- the column's dV (warpgroup 0) and dK (warpgroup 1), one key row per thread ----
-      mbar_wait(&bars->acc_full, it_cnt & 1, wc, 3);
+      const bool acc_ok = mbar_wait(&bars->acc_full, it_cnt & 1, wc, 3);
       tc_fence_after();
       {
         unsigned char* dst = reinterpret_cast<unsigned char*>(
@@ -301,7 +303,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         for (int ch = 0; ch < D / 32; ++ch) {
           tmem_ld32(tmem + lane_off + col + ch * 32, av);
           tmem_ld_wait();
-          if (r < c.keys) store_row32<T>(dst + ch * 64, av, sc);
+          if (acc_ok && r < c.keys) store_row32<T>(dst + ch * 64, av, sc);
         }
       }
       tc_fence_before();

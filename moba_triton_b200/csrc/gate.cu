@@ -25,14 +25,14 @@ __global__ void __launch_bounds__(128)
 pool_kernel(const T* __restrict__ k, const int32_t* __restrict__ cu, T* __restrict__ kbar,
             int packed, int tokens, int hkv, int d, int bs, int nb) {
   constexpr int EPV = 16 / sizeof(T);            // elements per 16-byte vector
-  const int blk = blockIdx.x;
-  const int seq = blockIdx.y / hkv, h = blockIdx.y % hkv;
+  const int blk = (int)(blockIdx.x % nb), kv_row = (int)(blockIdx.x / nb);
+  const int seq = kv_row / hkv, h = kv_row % hkv;
   const SeqSpan sp = seq_span(cu, packed, seq, tokens);
   const int vpr = d / EPV;                       // vectors per row
   const int groups = 128 / vpr;
   const int c = threadIdx.x % vpr, rg = threadIdx.x / vpr;
 
-  T* dst = kbar + ((size_t)blockIdx.y * nb + blk) * d;
+  T* dst = kbar + ((size_t)kv_row * nb + blk) * d;
   const int lo = blk * bs;
   if (lo >= sp.len) {                            // padded slot of a short packed sequence
     if (threadIdx.x < d) dst[threadIdx.x] = Elem<T>::from_f(0.f);
@@ -91,7 +91,9 @@ int launch_pool(const moba_b200_problem& p, const void* k, const int32_t* cu, vo
     set_error("pool: head_dim %d unsupported", p.head_dim);
     return MOBA_B200_EUNSUPPORTED;
   }
-  dim3 grid(p.num_blocks, p.n_seq * p.kv_heads);
+  const long long ctas = (long long)p.num_blocks * p.n_seq * p.kv_heads;
+  if (ctas > 0x7fffffffLL) { set_error("pool: %lld blocks exceed the grid limit", ctas); return MOBA_B200_EUNSUPPORTED; }
+  const unsigned grid = (unsigned)ctas;
 #define MOBA_POOL(T)                                                                   \
   pool_kernel<T><<<grid, 128, 0, st>>>((const T*)k, cu, (T*)kbar, p.packed, p.tokens,  \
                                        p.kv_heads, p.head_dim, p.block_size, p.num_blocks)
@@ -278,6 +280,10 @@ int launch_gate_portable(const moba_b200_problem& p, const void* q, const void* 
                       (size_t)kGateRows * (p.take > 0 ? p.take : 1) * 8;
   if (smem > 200 * 1024) {
     set_error("gate: head_dim %d / top_k %d need %zu bytes of shared memory", d, p.top_k, smem);
+    return MOBA_B200_EUNSUPPORTED;
+  }
+  if ((long long)p.n_seq * p.q_heads > 65535) {
+    set_error("portable gate: %d sequences x %d heads exceed 65535 grid rows", p.n_seq, p.q_heads);
     return MOBA_B200_EUNSUPPORTED;
   }
   dim3 grid((p.max_seqlen + kGateRows - 1) / kGateRows, p.n_seq * p.q_heads);

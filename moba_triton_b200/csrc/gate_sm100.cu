@@ -1,20 +1,24 @@
 // Gate scorer on tcgen05 tensor cores (bf16/f16, block_size 128, head_dim
 // 64/128, at most 8 ranked blocks per query).
 //
-// One CTA per (128-query tile, sequence, query head); with 128-token blocks a
-// tile is exactly one block, so every row of the tile has the same candidates:
-// the blocks before the tile's own. Roles:
-//   loader (1 thread)  TMA: the Q tile once, then block-mean chunks of 128 blocks
+// Persistent CTAs (two per SM) walk the (128-query tile, sequence, query head)
+// units, heaviest first, in alternating direction per round. With 128-token
+// blocks a tile is exactly one block, so every row of a tile has the same
+// candidates: the blocks before the tile's own. Roles:
+//   loader (1 thread)  TMA: the unit's Q tile, then block-mean chunks of 128 blocks
 //   mma    (1 thread)  S = Q Kbar^T (M128 N128 K=D) into one of two TMEM buffers
-//   select (2 x 4 warps, alternating chunks) tcgen05.ld one row per thread,
-//          round each score to the input dtype and pack it with its block id
-//          into one sortable 32-bit key (score bits made monotone in the high
-//          half, 0xFFFF - id in the low half), so "score descending, ties to
-//          the lower id" is plain integer order. Each thread keeps its best
-//          keys in a sorted register list; groups of four keys are skipped
-//          with one compare when none can enter.
-// At the end the two warpgroups' lists are merged and each thread emits its
-// ids plus the own block, ascending, -1 padded.
+//   select (2 x 4 warps, alternating chunks) tcgen05.ld, one row per thread.
+//          A score can enter a row's list only if it exceeds the score of the
+//          list's last entry (candidates arrive in ascending block order, so an
+//          equal score never wins). That test is one float compare per score;
+//          the few that pass are appended, by predicated stores, to a small
+//          per-thread buffer in shared memory, and the buffer is emptied into the
+//          row's sorted register list of L keys whenever some lane of the warp is
+//          about to run out of room. A key is the score rounded to the input dtype
+//          and made monotone in the high half and 0xFFFF - block id in the low half,
+//          so "score descending, ties to the lower id" is plain integer order.
+// At the end of a unit the two warpgroups' lists are merged and each thread emits
+// its ids plus the own block, ascending, -1 padded.
 //
 // Scores are float32 tensor-core sums rounded to the input dtype; the portable
 // gate rounds the exact sum. The two differ only when a float32 partial sum
@@ -41,11 +45,17 @@ constexpr int kEmpty = 0x7fffffff;
 template <int D> struct GateCfg {
   static constexpr int kSubs = D / 64;
   static constexpr int kOperand = kSubs * kSub;
-  static constexpr int kSmem = 3 * kOperand + 1024 + 512;     // Q + two Kbar stages
+  // Per-thread buffer of scores that passed the entry test, in slots of 8 bytes, and how
+  // many columns are tested between two checks for room. Two CTAs share an SM, which at
+  // head_dim 128 leaves room for 7 slots only.
+  static constexpr int kCap = (D == 64) ? 16 : 7;
+  static constexpr int kStep = (D == 64) ? 8 : 4;
+  static constexpr int kBufBytes = kCap * kTile * 8;                       // per warpgroup
+  static constexpr int kSmem = 3 * kOperand + 2 * kBufBytes + 1024 + 512;  // Q + two Kbar stages + buffers
 };
 
 struct Bars {
-  uint64_t q_full, kb_full[2], kb_empty[2], s_full[2], s_free[2], drain;
+  uint64_t q_full, q_free, kb_full[2], kb_empty[2], s_full[2], s_free[2], drain;
   uint32_t tmem_base;
   int abort;
 };
@@ -61,46 +71,77 @@ __device__ __forceinline__ void list_offer(uint32_t (&t)[L], uint32_t x) {
   }
 }
 
-// Two 16-bit floats (packed) -> two 16-bit keys whose unsigned order is the
-// numeric order: negative values have all bits flipped, the others only the sign.
-__device__ __forceinline__ uint32_t monotone16x2(uint32_t w) {
-  const uint32_t neg = ((w >> 15) & 0x00010001u) * 0x7FFFu;
-  return w ^ (neg | 0x80008000u);
+template <typename T> __device__ __forceinline__ uint32_t round16(float a);
+template <> __device__ __forceinline__ uint32_t round16<__nv_bfloat16>(float a) {
+  return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(a));
+}
+template <> __device__ __forceinline__ uint32_t round16<__half>(float a) {
+  return (uint32_t)__half_as_ushort(__float2half_rn(a));
+}
+template <typename T> __device__ __forceinline__ float widen16(uint32_t bits);
+template <> __device__ __forceinline__ float widen16<__nv_bfloat16>(uint32_t bits) { return __uint_as_float(bits << 16); }
+template <> __device__ __forceinline__ float widen16<__half>(uint32_t bits) {
+  return __half2float(__ushort_as_half((unsigned short)bits));
 }
 
-template <typename T> __device__ __forceinline__ uint32_t round_pack2(float a, float b);
-template <> __device__ __forceinline__ uint32_t round_pack2<__nv_bfloat16>(float a, float b) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&v);
+// Score (rounded to T) and block id -> sortable key; never 0 for a real candidate
+// (the low half of a key is 0xFFFF - id with id <= 0xFFFE).
+template <typename T>
+__device__ __forceinline__ uint32_t make_key(float score, uint32_t block) {
+  const uint32_t b = round16<T>(score);
+  const uint32_t mono = (b & 0x8000u) ? (~b & 0xFFFFu) : (b | 0x8000u);
+  return (mono << 16) | (0xFFFFu - block);
 }
-template <> __device__ __forceinline__ uint32_t round_pack2<__half>(float a, float b) {
-  __half2 v = __floats2half2_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&v);
+// The score a candidate has to exceed to get past `key` (the list's last entry):
+// -inf while the list has room.
+template <typename T>
+__device__ __forceinline__ float entry_bar(uint32_t key) {
+  if (key == 0u) return -INFINITY;
+  const uint32_t mono = key >> 16;
+  const uint32_t b = (mono & 0x8000u) ? (mono & 0x7FFFu) : (~mono & 0xFFFFu);
+  return widen16<T>(b);
+}
+
+// Which unit a CTA takes in its `round`-th turn: heaviest units first, alternating
+// direction, so that no CTA collects the heaviest unit of every round.
+__device__ __forceinline__ int unit_of(int round) {
+  const int g = (int)gridDim.x, c = (int)blockIdx.x;
+  return round * g + ((round & 1) ? (g - 1 - c) : c);
+}
+
+struct Unit {
+  int tile, seq, hq, row0, n_chunks, bos, len;
+};
+__device__ __forceinline__ bool load_unit(Unit& u, int idx, const moba_b200_problem& p, const int32_t* cu,
+                                          int n_tiles) {
+  const int ny = p.n_seq * p.q_heads;
+  u.tile = n_tiles - 1 - idx / ny;                              // long tiles first
+  const int y = idx % ny;
+  u.seq = y / p.q_heads; u.hq = y % p.q_heads;
+  const SeqSpan sp = seq_span(cu, p.packed, u.seq, p.tokens);
+  u.bos = sp.bos; u.len = sp.len;
+  u.row0 = u.tile * kTile;
+  u.n_chunks = (p.take > 0) ? (u.tile + kTile - 1) / kTile : 0;   // candidates: blocks [0, tile)
+  return u.row0 < sp.len;
 }
 
 template <int D, typename T, int L>
 __global__ void __launch_bounds__(kThreads, 2)
 gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kb_map,
                   const int32_t* __restrict__ cu, int32_t* __restrict__ block_idx, moba_b200_problem p,
-                  int n_tiles, unsigned* error_word) {
+                  int n_tiles, int n_units, unsigned* error_word) {
   using Cfg = GateCfg<D>;
+  constexpr int CAP = Cfg::kCap, STEP = Cfg::kStep;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   unsigned char* sQ = smem;
   unsigned char* sKb = sQ + Cfg::kOperand;                    // two stages
-  Bars* bars = reinterpret_cast<Bars*>(sKb + 2 * Cfg::kOperand);
+  unsigned char* sBuf = sKb + 2 * Cfg::kOperand;              // two warpgroups' buffers
+  Bars* bars = reinterpret_cast<Bars*>(sBuf + 2 * Cfg::kBufBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = n_tiles - 1 - (int)blockIdx.x;             // long tiles first
-  const int seq = blockIdx.y / p.q_heads, hq = blockIdx.y % p.q_heads;
-  const SeqSpan sp = seq_span(cu, p.packed, seq, p.tokens);
-  const int row0 = tile * kTile;
-  if (row0 >= sp.len) return;                                 // whole CTA leaves before any barrier
   const int group = p.q_heads / p.kv_heads;
-  const int kv_row = seq * p.kv_heads + hq / group;
-  const size_t b = p.packed ? 0 : (size_t)seq;
   const int take = p.take;
-  const int n_chunks = (take > 0) ? (tile + kTile - 1) / kTile : 0;   // candidates: blocks [0, tile)
 #ifdef MOBA_WAIT_STATS
   const WaitCtx wc{&bars->abort, error_word, nullptr};
 #else
@@ -108,7 +149,7 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
 #endif
 
   if (threadIdx.x == 0) {
-    mbar_init(&bars->q_full, 1);
+    mbar_init(&bars->q_full, 1); mbar_init(&bars->q_free, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->kb_full[i], 1); mbar_init(&bars->kb_empty[i], 1);
       mbar_init(&bars->s_full[i], 1); mbar_init(&bars->s_free[i], 128);
@@ -124,117 +165,149 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
 
+  // Every role walks the same units and counts the same chunks: `gc` is the number of
+  // chunks of all earlier units of this CTA, and chunk c of a unit uses Kbar stage and
+  // TMEM buffer (gc + c) & 1.
   if (warp < 8) {
     // ================================ select ================================
     const int wg = warp >> 2;
     const int r = (warp & 3) * 32 + lane;
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
-    uint32_t best[L];
+    // This thread's buffer: slot s is the 8 bytes at buf0 + s * kSlot (shared-memory address).
+    constexpr uint32_t kSlot = kTile * 8;
+    const uint32_t buf0 = smem_u32(sBuf + wg * Cfg::kBufBytes) + (uint32_t)r * 8u;
+    // List exchange at the end of a unit: thread r of warpgroup 1 leaves its list in the
+    // (empty) buffer slots of thread r of warpgroup 0, two keys per slot, so a thread of
+    // warpgroup 0 only ever reads and overwrites words of its own.
+    const uint32_t xk0 = smem_u32(sBuf) + (uint32_t)r * 8u;
+    static_assert((L + 1) / 2 <= CAP, "a list fits the slots of one thread");
+    uint32_t gc = 0, used = 0;                                  // used: chunks this warpgroup has taken so far
+    for (int round = 0; round * (int)gridDim.x < n_units; ++round) {
+      const int ui = unit_of(round);
+      if (ui >= n_units) continue;
+      Unit u;
+      if (!load_unit(u, ui, p, cu, n_tiles)) continue;
+      uint32_t best[L];
 #pragma unroll
-    for (int e = 0; e < L; ++e) best[e] = 0u;                   // 0 sorts below every real key
-    // The two warpgroups take alternate chunks of the same 128 rows, so each keeps
-    // its own list per row; the lists are merged at the end through shared memory.
-    for (int c = wg; c < n_chunks; c += 2) {
-      const uint32_t u = (uint32_t)c >> 1;
-      mbar_wait(&bars->s_full[wg], u & 1, wc);
-      tc_fence_after();
-      const int c0 = c * kTile;
-      const int cmax = tile - c0;                               // columns [0, cmax) are candidates
-      const bool full = cmax >= kTile;
-      uint32_t v[32];
-#pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
-        tmem_ld32(tmem + lane_off + wg * 128 + ch * 32, v);
-        tmem_ld_wait();
-        const uint32_t inv0 = 0xFFFFu - (uint32_t)(c0 + ch * 32);   // low half of column 0's key
-#pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          const uint32_t w0 = monotone16x2(round_pack2<T>(__uint_as_float(v[g * 4 + 0]), __uint_as_float(v[g * 4 + 1])));
-          const uint32_t w1 = monotone16x2(round_pack2<T>(__uint_as_float(v[g * 4 + 2]), __uint_as_float(v[g * 4 + 3])));
-          uint32_t k0 = (w0 << 16) | (inv0 - (g * 4 + 0));
-          uint32_t k1 = (w0 & 0xFFFF0000u) | (inv0 - (g * 4 + 1));
-          uint32_t k2 = (w1 << 16) | (inv0 - (g * 4 + 2));
-          uint32_t k3 = (w1 & 0xFFFF0000u) | (inv0 - (g * 4 + 3));
-          if (!full) {
-            const int col = ch * 32 + g * 4;
-            k0 = (col + 0 < cmax) ? k0 : 0u;
-            k1 = (col + 1 < cmax) ? k1 : 0u;
-            k2 = (col + 2 < cmax) ? k2 : 0u;
-            k3 = (col + 3 < cmax) ? k3 : 0u;
+      for (int e = 0; e < L; ++e) best[e] = 0u;                 // 0 sorts below every real key
+      float bar = -INFINITY;                                    // a score must exceed this to be appended
+      uint32_t wa = buf0;                                       // address of the next free slot
+      auto flush = [&]() {                                      // whole warp: empty the buffers into the lists
+        while (__any_sync(0xffffffffu, wa != buf0)) {
+          uint32_t key = 0u;
+          if (wa != buf0) {
+            wa -= kSlot;
+            uint32_t sx, sy;
+            asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(sx), "=r"(sy) : "r"(wa));
+            key = make_key<T>(__uint_as_float(sx), sy);
           }
-          // Mostly at most one key of a group enters the list: offer the largest, and the
-          // other three only if one of them still beats the list's last entry. Keys are
-          // distinct (the column is in the low half), so exactly one equals the maximum.
-          const uint32_t m = max(max(k0, k1), max(k2, k3));
-          if (m > best[L - 1]) {
-            list_offer<L>(best, m);
-            k0 = (k0 == m) ? 0u : k0;
-            k1 = (k1 == m) ? 0u : k1;
-            k2 = (k2 == m) ? 0u : k2;
-            k3 = (k3 == m) ? 0u : k3;
-            if (max(max(k0, k1), max(k2, k3)) > best[L - 1]) {
-              list_offer<L>(best, k0);
-              list_offer<L>(best, k1);
-              list_offer<L>(best, k2);
-              list_offer<L>(best, k3);
+          list_offer<L>(best, key);
+        }
+        bar = entry_bar<T>(best[L - 1]);
+      };
+      // the two warpgroups take alternate chunks of the same 128 rows
+      for (int c = (int)((wg - gc) & 1u); c < u.n_chunks; c += 2, ++used) {
+        const bool s_ok = mbar_wait(&bars->s_full[wg], used & 1, wc);
+        tc_fence_after();
+        const int c0 = c * kTile;
+        const int cmax = u.tile - c0;                           // columns [0, cmax) are candidates
+        const bool full = cmax >= kTile;
+        const bool run = __all_sync(0xffffffffu, s_ok);         // a wait gave up: rank nothing unseen
+        uint32_t v[32];
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ++ch) {
+          tmem_ld32(tmem + lane_off + wg * 128 + ch * 32, v);
+          tmem_ld_wait();
+          if (ch == 3) { tc_fence_before(); mbar_arrive(&bars->s_free[wg]); }   // the scores are in registers
+          if (!run || ch * 32 >= cmax) continue;
+          if (!full) {
+#pragma unroll
+            for (int k = 0; k < 32; ++k)
+              if (ch * 32 + k >= cmax) v[k] = 0xff800000u;      // -inf: never passes
+          }
+#pragma unroll
+          for (int k0 = 0; k0 < 32; k0 += STEP) {
+            if (__any_sync(0xffffffffu, wa > buf0 + (CAP - STEP) * kSlot)) flush();   // room for STEP more
+#pragma unroll
+            for (int k = k0; k < k0 + STEP; ++k) {
+              if (__uint_as_float(v[k]) > bar) {
+                asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(wa), "r"(v[k]), "r"((uint32_t)(c0 + ch * 32 + k)) : "memory");
+                wa += kSlot;
+              }
             }
           }
         }
       }
-      tc_fence_before();
-      mbar_arrive(&bars->s_free[wg]);
-    }
-    // ---- merge the two warpgroups' lists (warpgroup 1 -> shared -> warpgroup 0) ----
-    uint32_t* xk = reinterpret_cast<uint32_t*>(sKb);            // the Kbar stages are idle by now
-    asm volatile("bar.sync 2, 256;" ::: "memory");              // every S MMA has been consumed
-    if (wg == 1) {
+      flush();
+      gc += (uint32_t)u.n_chunks;
+      // ---- merge the two warpgroups' lists (warpgroup 1 -> warpgroup 0's empty buffer) ----
+      asm volatile("bar.sync 2, 256;" ::: "memory");            // warpgroup 0 has emptied its buffer
+      if (wg == 1) {
 #pragma unroll
-      for (int e = 0; e < L; ++e) xk[e * kTile + r] = best[e];
-    }
-    asm volatile("bar.sync 2, 256;" ::: "memory");
-    if (wg == 0 && row0 + r < sp.len) {
-#pragma unroll
-      for (int e = 0; e < L; ++e) list_offer<L>(best, xk[e * kTile + r]);
-      // ---- emit: the best `take` ids plus the own block, ascending, -1 padded ----
-      int ids[L];
-      int kept = 0;
-#pragma unroll
-      for (int e = 0; e < L; ++e) {
-        const bool ok = e < take && best[e] != 0u;
-        ids[e] = ok ? (int)(0xFFFFu - (best[e] & 0xFFFFu)) : kEmpty;
-        kept += ok ? 1 : 0;
+        for (int e = 0; e < L; ++e)
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(xk0 + (uint32_t)(e >> 1) * kSlot + (uint32_t)(e & 1) * 4u), "r"(best[e]) : "memory");
       }
-      int32_t* dst = block_idx + ((b * p.q_heads + hq) * p.tokens + sp.bos + row0 + r) * (size_t)p.slots;
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      if (wg == 0 && u.row0 + r < u.len) {
 #pragma unroll
-      for (int e = 0; e < L; ++e) {                             // rank by id: position in the output
-        if (ids[e] == kEmpty) continue;
-        int rank = 0;
+        for (int e = 0; e < L; ++e) {
+          uint32_t other;
+          asm volatile("ld.shared.b32 %0, [%1];" : "=r"(other) : "r"(xk0 + (uint32_t)(e >> 1) * kSlot + (uint32_t)(e & 1) * 4u));
+          list_offer<L>(best, other);
+        }
+        // ---- emit: the best `take` ids plus the own block, ascending, -1 padded ----
+        int ids[L];
+        int kept = 0;
 #pragma unroll
-        for (int f = 0; f < L; ++f) rank += (ids[f] < ids[e]) ? 1 : 0;
-        dst[rank] = ids[e];
+        for (int e = 0; e < L; ++e) {
+          const bool ok = e < take && best[e] != 0u;
+          ids[e] = ok ? (int)(0xFFFFu - (best[e] & 0xFFFFu)) : kEmpty;
+          kept += ok ? 1 : 0;
+        }
+        const size_t b = p.packed ? 0 : (size_t)u.seq;
+        int32_t* dst = block_idx + ((b * p.q_heads + u.hq) * p.tokens + u.bos + u.row0 + r) * (size_t)p.slots;
+#pragma unroll
+        for (int e = 0; e < L; ++e) {                           // rank by id: position in the output
+          if (ids[e] == kEmpty) continue;
+          int rank = 0;
+#pragma unroll
+          for (int f = 0; f < L; ++f) rank += (ids[f] < ids[e]) ? 1 : 0;
+          dst[rank] = ids[e];
+        }
+        if (p.always_current) dst[kept++] = u.tile;             // the own block is past every candidate
+        for (int e = kept; e < p.slots; ++e) dst[e] = -1;
       }
-      if (p.always_current) dst[kept++] = tile;                 // the own block is past every candidate
-      for (int e = kept; e < p.slots; ++e) dst[e] = -1;
+      // Warpgroup 0 reads the exchange area (its own buffer) before it appends to it again;
+      // warpgroup 1 writes there only behind the first barrier of the next unit.
     }
   } else if (warp == kMmaWarp) {
-    if (lane == 0 && n_chunks > 0) {
+    if (lane == 0) {
       const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
       const uint32_t idesc = make_idesc(0, 128, 128, 0, 0) | (fmt << 7) | (fmt << 10);
       const uint32_t aQ = smem_u32(sQ);
-      mbar_wait(&bars->q_full, 0, wc);
-      for (int c = 0; c < n_chunks; ++c) {
-        const uint32_t st = c & 1, u = (uint32_t)c >> 1;
-        const uint32_t aK = smem_u32(sKb) + st * Cfg::kOperand;
-        mbar_wait(&bars->kb_full[st], u & 1, wc);
-        if (u >= 1) mbar_wait(&bars->s_free[st], (u - 1) & 1, wc);
-        tc_fence_after();
+      uint32_t gc = 0, nq = 0;                                  // chunks / Q tiles consumed so far
+      for (int round = 0; round * (int)gridDim.x < n_units; ++round) {
+        const int ui = unit_of(round);
+        if (ui >= n_units) continue;
+        Unit u;
+        if (!load_unit(u, ui, p, cu, n_tiles) || u.n_chunks == 0) continue;
+        mbar_wait(&bars->q_full, nq & 1, wc);
+        for (int c = 0; c < u.n_chunks; ++c, ++gc) {
+          const uint32_t st = gc & 1, use = gc >> 1;
+          const uint32_t aK = smem_u32(sKb) + st * Cfg::kOperand;
+          mbar_wait(&bars->kb_full[st], use & 1, wc);
+          if (use >= 1) mbar_wait(&bars->s_free[st], (use - 1) & 1, wc);
+          tc_fence_after();
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t o = (ks >> 2) * kSub + (ks & 3) * 32;
-          umma_f16(tmem + st * 128, make_sdesc(aQ + o, 16, 1024), make_sdesc(aK + o, 16, 1024), idesc, ks > 0);
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint32_t o = (ks >> 2) * kSub + (ks & 3) * 32;
+            umma_f16(tmem + st * 128, make_sdesc(aQ + o, 16, 1024), make_sdesc(aK + o, 16, 1024), idesc, ks > 0);
+          }
+          umma_commit(&bars->s_full[st]);
+          umma_commit(&bars->kb_empty[st]);
         }
-        umma_commit(&bars->s_full[st]);
-        umma_commit(&bars->kb_empty[st]);
+        umma_commit(&bars->q_free);                             // the Q tile may be replaced
+        ++nq;
       }
       // Every MMA has completed before the CTA lets go of its TMEM, also on the way out of
       // a run that gave up on a wait.
@@ -243,25 +316,36 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     }
     __syncwarp();
   } else {
-    if (lane == 0 && n_chunks > 0) {
-      const int tok0 = (int)(b * p.tokens) + sp.bos + row0;
-      mbar_expect_tx(&bars->q_full, Cfg::kOperand);
-      for (int s = 0; s < Cfg::kSubs; ++s) tma_load_3d(sQ + s * kSub, &q_map, &bars->q_full, s * 64, hq, tok0);
-      int issued = 0;
-      for (int c = 0; c < n_chunks; ++c) {
-        const uint32_t st = c & 1, u = (uint32_t)c >> 1;
-        if (u >= 1) mbar_wait(&bars->kb_empty[st], (u - 1) & 1, wc);
-        if (*wc.abort) break;                            // no new loads once a wait gave up
-        mbar_expect_tx(&bars->kb_full[st], Cfg::kOperand);
-        for (int s = 0; s < Cfg::kSubs; ++s)
-          tma_load_3d(sKb + st * Cfg::kOperand + s * kSub, &kb_map, &bars->kb_full[st], s * 64, c * kTile, kv_row);
-        issued = c + 1;
+    if (lane == 0) {
+      uint32_t gc = 0, nq = 0;
+      for (int round = 0; round * (int)gridDim.x < n_units; ++round) {
+        const int ui = unit_of(round);
+        if (ui >= n_units) continue;
+        Unit u;
+        if (!load_unit(u, ui, p, cu, n_tiles) || u.n_chunks == 0) continue;
+        if (*wc.abort) break;                                   // no new loads once a wait gave up
+        const size_t b = p.packed ? 0 : (size_t)u.seq;
+        const int kv_row = u.seq * p.kv_heads + u.hq / group;
+        const int tok0 = (int)(b * p.tokens) + u.bos + u.row0;
+        if (nq >= 1) mbar_wait(&bars->q_free, (nq - 1) & 1, wc);
+        mbar_expect_tx(&bars->q_full, Cfg::kOperand);
+        for (int s = 0; s < Cfg::kSubs; ++s) tma_load_3d(sQ + s * kSub, &q_map, &bars->q_full, s * 64, u.hq, tok0);
+        ++nq;
+        for (int c = 0; c < u.n_chunks; ++c, ++gc) {
+          const uint32_t st = gc & 1, use = gc >> 1;
+          if (use >= 1) mbar_wait(&bars->kb_empty[st], (use - 1) & 1, wc);
+          if (*wc.abort) break;
+          mbar_expect_tx(&bars->kb_full[st], Cfg::kOperand);
+          for (int s = 0; s < Cfg::kSubs; ++s)
+            tma_load_3d(sKb + st * Cfg::kOperand + s * kSub, &kb_map, &bars->kb_full[st], s * 64, c * kTile, kv_row);
+        }
+        if (*wc.abort) break;
       }
       // No load may be in flight into this CTA's shared memory when it exits.
-      mbar_wait_quiet(&bars->q_full, 0);
-      for (int k = 1; k <= 2 && k <= issued; ++k) {
-        const int c = issued - k;
-        mbar_wait_quiet(&bars->kb_full[c & 1], ((uint32_t)c >> 1) & 1);
+      if (nq >= 1) mbar_wait_quiet(&bars->q_full, (nq - 1) & 1);
+      for (uint32_t k = 1; k <= 2 && k <= gc; ++k) {
+        const uint32_t c = gc - k;
+        mbar_wait_quiet(&bars->kb_full[c & 1], (c >> 1) & 1);
       }
     }
     __syncwarp();
@@ -279,8 +363,12 @@ int launch_one(const moba_b200_problem& p, const CUtensorMap& qm, const CUtensor
   auto kern = gate_sm100_kernel<D, T, L>;
   MOBA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GateCfg<D>::kSmem));
   const int n_tiles = (p.max_seqlen + kTile - 1) / kTile;
-  dim3 grid(n_tiles, p.n_seq * p.q_heads);
-  kern<<<grid, kThreads, GateCfg<D>::kSmem, st>>>(qm, km, cu, block_idx, p, n_tiles, err);
+  const long long n_units = (long long)n_tiles * p.n_seq * p.q_heads;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = (int)(n_units < 2LL * sms ? n_units : 2LL * sms);
+  kern<<<grid, kThreads, GateCfg<D>::kSmem, st>>>(qm, km, cu, block_idx, p, n_tiles, (int)n_units, err);
   MOBA_LAUNCH_OK("gate_sm100_kernel");
   return MOBA_B200_OK;
 }
@@ -291,7 +379,8 @@ bool gate_sm100_supported(const moba_b200_problem& p) {
   return (p.dtype == MOBA_B200_BF16 || p.dtype == MOBA_B200_F16) && p.block_size == 128 &&
          (p.head_dim == 64 || p.head_dim == 128) && p.take <= kMaxTake && p.slots <= kMaxTake + 1 &&
          p.num_blocks <= 0xFFFF &&
-         (long long)p.batch * p.tokens < 0x7fffffffLL;
+         (long long)p.batch * p.tokens < 0x7fffffffLL &&
+         (long long)((p.max_seqlen + 127) / 128) * p.n_seq * p.q_heads < 0x7fffffffLL;
 }
 
 int encode_kbar_map_impl(CUtensorMap* out, const void* base, uint64_t kv_rows, uint64_t nb, uint64_t dim);

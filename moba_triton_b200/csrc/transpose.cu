@@ -9,9 +9,11 @@
 //   3. offsets  per (sequence, kv head): exclusive scan over blocks ->
 //               col_offsets, and the longest-first dispatch order (stable
 //               descending sort of col_nnz, by rank counting)
-//   4. scatter  one warp per (row chunk, sequence, query head): walks its rows in
-//               order, ranks equal blocks inside the warp with match.any and
-//               writes (row, head, slot) at cursor[block]++.
+//   4. scatter  one CTA per (row chunk, sequence, query head): its warps split the
+//               chunk's rows into consecutive runs; a per-warp histogram and a scan
+//               over the warps give each warp its own cursors, and every warp then
+//               walks its run in order, ranks equal blocks inside the warp with
+//               match.any and writes (row, head, slot) at cursor[block]++.
 //
 // Stands in for count_columns_kernel / offsets_and_order_kernel /
 // scatter_pairs_kernel of the reference (src/moba/kernels/routing.py:138-301),
@@ -48,8 +50,8 @@ __global__ void __launch_bounds__(256)
 count_kernel(const int32_t* __restrict__ block_idx, const int32_t* __restrict__ cu,
              int32_t* __restrict__ tile_counts, moba_b200_problem p, int R, int C) {
   extern __shared__ int hist[];
-  const int chunk = blockIdx.x;
-  const int seq = blockIdx.y / p.q_heads, hq = blockIdx.y % p.q_heads;
+  const int chunk = blockIdx.x % C, y = blockIdx.x / C;
+  const int seq = y / p.q_heads, hq = y % p.q_heads;
   const SeqSpan sp = seq_span(cu, p.packed, seq, p.tokens);
   const int row0 = chunk * R;
   if (row0 >= sp.len) return;
@@ -74,13 +76,14 @@ count_kernel(const int32_t* __restrict__ block_idx, const int32_t* __restrict__ 
 // prefix (in (g, chunk) order) and writes the column total.
 __global__ void __launch_bounds__(128)
 colscan_kernel(const int32_t* __restrict__ cu, int32_t* __restrict__ tile_counts,
-               int32_t* __restrict__ col_nnz, moba_b200_problem p, int R, int C) {
+               int32_t* __restrict__ col_nnz, moba_b200_problem p, int R, int C, int ctas_per_row) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int col = blockIdx.x * 4 + warp;
+  const int col = (int)(blockIdx.x % ctas_per_row) * 4 + warp;
+  const int kv_row = (int)(blockIdx.x / ctas_per_row);       // (sequence, kv head)
   if (col >= p.num_blocks) return;
-  const int seq = blockIdx.y / p.kv_heads;
+  const int seq = kv_row / p.kv_heads;
   const SeqSpan sp = seq_span(cu, p.packed, seq, p.tokens);
-  int32_t* out_nnz = col_nnz + (size_t)blockIdx.y * p.num_blocks + col;
+  int32_t* out_nnz = col_nnz + (size_t)kv_row * p.num_blocks + col;
   if ((size_t)col * p.block_size >= (size_t)sp.len) {
     if (lane == 0) *out_nnz = 0;
     return;
@@ -89,7 +92,7 @@ colscan_kernel(const int32_t* __restrict__ cu, int32_t* __restrict__ tile_counts
   const int c_lo = (int)(((size_t)col * p.block_size) / R);
   const int c_hi = (sp.len + R - 1) / R;                    // exclusive
   const int span = c_hi - c_lo;
-  int32_t* base = tile_counts + ((size_t)blockIdx.y * p.num_blocks + col) * (group * C);
+  int32_t* base = tile_counts + ((size_t)kv_row * p.num_blocks + col) * (group * C);
   int running = 0;
   const int total = group * span;
   for (int i0 = 0; i0 < total; i0 += 32) {
@@ -173,24 +176,25 @@ offsets_order_kernel(const int32_t* __restrict__ col_nnz, int32_t* __restrict__ 
   if (i < nb && part == 0) ord[rank] = i;
 }
 
-// One warp per (row chunk, sequence, query head); four chunks (warps) per CTA, each with its
-// own cursor array, so that enough warps are resident to cover the latency of the
-// dependent match / cursor / store chain.
-constexpr int kScatterWarps = 4;
-__global__ void __launch_bounds__(32 * kScatterWarps)
+// One CTA of W warps per (row chunk, sequence, query head). The walk of a run is one
+// dependent chain per warp (match, cursor, store), so the chunk is cut into W runs that are
+// walked side by side: a histogram per run and a scan over the runs (both in shared memory)
+// turn the chunk's cursors into cursors per run. The order inside a column stays
+// (query head, row): runs are consecutive rows and keep the chunk's order.
+template <int W>
+__global__ void __launch_bounds__(32 * W)
 scatter_kernel(const int32_t* __restrict__ block_idx, const int32_t* __restrict__ cu,
                const int32_t* __restrict__ tile_prefix, const int32_t* __restrict__ col_offsets,
                int32_t* __restrict__ rows_out, int32_t* __restrict__ heads_out,
                int32_t* __restrict__ slots_out, moba_b200_problem p, int R, int C,
                long long capacity) {
-  extern __shared__ int cursor_all[];
+  extern __shared__ int cursor_all[];                        // [W][nb_lim]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int* cursor = cursor_all + warp * p.num_blocks;
-  const int chunk = blockIdx.x * kScatterWarps + warp;
-  const int seq = blockIdx.y / p.q_heads, hq = blockIdx.y % p.q_heads;
+  const int chunk = blockIdx.x % C, y = blockIdx.x / C;
+  const int seq = y / p.q_heads, hq = y % p.q_heads;
   const SeqSpan sp = seq_span(cu, p.packed, seq, p.tokens);
   const int row0 = chunk * R;
-  if (chunk >= C || row0 >= sp.len) return;
+  if (row0 >= sp.len) return;                                // the whole CTA
   const int rows = min(R, sp.len - row0);
   const int nb_lim = (row0 + rows - 1) / p.block_size + 1;
   const int group = p.q_heads / p.kv_heads;
@@ -198,18 +202,39 @@ scatter_kernel(const int32_t* __restrict__ block_idx, const int32_t* __restrict_
   const size_t kv_row = (size_t)seq * p.kv_heads + kvh;
   const int32_t* pre = tile_prefix + (kv_row * p.num_blocks) * (group * C) + g * C + chunk;
   const int32_t* off = col_offsets + kv_row * (p.num_blocks + 1);
-  for (int i = lane; i < nb_lim; i += 32) cursor[i] = off[i] + pre[(size_t)i * (group * C)];
-  __syncwarp();
-  const int32_t* src = block_idx + block_idx_row(p, seq, hq, sp.bos, row0);
+  // this warp's run of rows
+  const int run = (rows + W - 1) / W;
+  const int r_lo = min(rows, warp * run), r_hi = min(rows, r_lo + run);
+  const int32_t* src = block_idx + block_idx_row(p, seq, hq, sp.bos, row0 + r_lo);
+  const int n = (r_hi - r_lo) * p.slots;
+  int* cursor = cursor_all + warp * nb_lim;
+
+  for (int i = threadIdx.x; i < W * nb_lim; i += 32 * W) cursor_all[i] = 0;
+  __syncthreads();
+  for (int e = lane; e < n; e += 32) {
+    const int blk = src[e];
+    if (blk >= 0 && blk < nb_lim) atomicAdd(&cursor[blk], 1);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < nb_lim; i += 32 * W) {
+    int at = off[i] + pre[(size_t)i * (group * C)];
+#pragma unroll
+    for (int w = 0; w < W; ++w) {
+      const int t = cursor_all[w * nb_lim + i];
+      cursor_all[w * nb_lim + i] = at;
+      at += t;
+    }
+  }
+  __syncthreads();
+
   int32_t* ro = rows_out + kv_row * capacity;
   int32_t* ho = heads_out + kv_row * capacity;
   int32_t* so = slots_out + kv_row * capacity;
-  const int n = rows * p.slots;
   const unsigned lt = (1u << lane) - 1u;
-  // The walk is one long dependent chain per warp (match, cursor, store), and few warps are
-  // resident when there are few heads, so the entries are fetched a batch of kBatch steps
-  // ahead: one memory latency per batch instead of one per step.
-  constexpr int kBatch = 8;
+  const int first_row = sp.bos + row0 + r_lo;
+  // The entries are fetched a batch of kBatch steps ahead: one memory latency per batch
+  // instead of one per step.
+  constexpr int kBatch = 4;
   int nxt[kBatch];
 #pragma unroll
   for (int j = 0; j < kBatch; ++j) {
@@ -240,13 +265,27 @@ scatter_kernel(const int32_t* __restrict__ block_idx, const int32_t* __restrict_
       if (valid) {
         const long long dst = base + __popc(same & lt);
         if (dst < capacity) {
-          ro[dst] = sp.bos + row0 + e / p.slots;
+          ro[dst] = first_row + e / p.slots;
           ho[dst] = hq;
           so[dst] = e % p.slots;
         }
       }
     }
   }
+}
+
+template <int W>
+static int launch_scatter(const moba_b200_problem& p, const int32_t* block_idx, const int32_t* cu,
+                          const int32_t* tiles, const int32_t* col_offsets, int32_t* rows, int32_t* heads,
+                          int32_t* slots, const TransposeGeom& g, long long capacity, cudaStream_t st) {
+  const size_t smem = (size_t)W * p.num_blocks * sizeof(int);
+  if (smem > 48 * 1024)
+    MOBA_CUDA_OK(cudaFuncSetAttribute(scatter_kernel<W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const long long ctas = (long long)g.chunks * p.n_seq * p.q_heads;
+  scatter_kernel<W><<<(unsigned)ctas, 32 * W, smem, st>>>(block_idx, cu, tiles, col_offsets, rows, heads, slots, p,
+                                                           g.chunk_rows, g.chunks, capacity);
+  MOBA_LAUNCH_OK("scatter_kernel");
+  return MOBA_B200_OK;
 }
 
 int launch_transpose(const moba_b200_problem& p, const int32_t* block_idx, const int32_t* cu,
@@ -260,8 +299,13 @@ int launch_transpose(const moba_b200_problem& p, const int32_t* block_idx, const
     return MOBA_B200_ESCRATCH;
   }
   const size_t hist_bytes = (size_t)p.num_blocks * sizeof(int);
-  if (kScatterWarps * hist_bytes > 200 * 1024) {
+  if (hist_bytes > 200 * 1024) {
     set_error("transpose: %d blocks per sequence exceed the shared-memory histogram", p.num_blocks);
+    return MOBA_B200_EUNSUPPORTED;
+  }
+  const long long row_ctas = (long long)g.chunks * p.n_seq * p.q_heads;
+  if (row_ctas > 0x7fffffffLL) {
+    set_error("transpose: %lld (row chunk, sequence, head) units exceed the grid limit", row_ctas);
     return MOBA_B200_EUNSUPPORTED;
   }
   int32_t* tiles = static_cast<int32_t*>(scratch);
@@ -269,30 +313,24 @@ int launch_transpose(const moba_b200_problem& p, const int32_t* block_idx, const
   const long long capacity = (long long)group * p.max_seqlen * p.slots;
   if (hist_bytes > 48 * 1024) {
     MOBA_CUDA_OK(cudaFuncSetAttribute(count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hist_bytes));
-    // handled below: the scatter kernel holds one cursor array per warp
     MOBA_CUDA_OK(cudaFuncSetAttribute(offsets_order_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hist_bytes));
   }
-  if (kScatterWarps * hist_bytes > 48 * 1024)
-    MOBA_CUDA_OK(cudaFuncSetAttribute(scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)(kScatterWarps * hist_bytes)));
-  dim3 grid_rows(g.chunks, p.n_seq * p.q_heads);
   { KernelTimer t__("count_kernel", st);
-  count_kernel<<<grid_rows, 256, hist_bytes, st>>>(block_idx, cu, tiles, p, g.chunk_rows, g.chunks);
+  count_kernel<<<(unsigned)row_ctas, 256, hist_bytes, st>>>(block_idx, cu, tiles, p, g.chunk_rows, g.chunks);
   MOBA_LAUNCH_OK("count_kernel"); }
-  dim3 grid_cols((p.num_blocks + 3) / 4, p.n_seq * p.kv_heads);
   { KernelTimer t__("colscan_kernel", st);
-  colscan_kernel<<<grid_cols, 128, 0, st>>>(cu, tiles, col_nnz, p, g.chunk_rows, g.chunks);
+  const unsigned per_row = (unsigned)((p.num_blocks + 3) / 4);
+  colscan_kernel<<<per_row * (unsigned)(p.n_seq * p.kv_heads), 128, 0, st>>>(cu, tiles, col_nnz, p, g.chunk_rows, g.chunks, (int)per_row);
   MOBA_LAUNCH_OK("colscan_kernel"); }
   { KernelTimer t__("offsets_order_kernel", st);
   offsets_order_kernel<<<dim3(p.n_seq * p.kv_heads, (p.num_blocks + 127) / 128), 1024, hist_bytes, st>>>(
       col_nnz, col_offsets, order, p.num_blocks);
   MOBA_LAUNCH_OK("offsets_order_kernel"); }
   { KernelTimer t__("scatter_kernel", st);
-  dim3 grid_scatter((g.chunks + kScatterWarps - 1) / kScatterWarps, p.n_seq * p.q_heads);
-  scatter_kernel<<<grid_scatter, 32 * kScatterWarps, kScatterWarps * hist_bytes, st>>>(
-      block_idx, cu, tiles, col_offsets, rows, heads, slots, p, g.chunk_rows, g.chunks, capacity);
-  MOBA_LAUNCH_OK("scatter_kernel"); }
-  return MOBA_B200_OK;
+  // as many warps per chunk as their cursor arrays leave room for several CTAs per SM
+  if (8 * hist_bytes <= 64 * 1024) return launch_scatter<8>(p, block_idx, cu, tiles, col_offsets, rows, heads, slots, g, capacity, st);
+  if (4 * hist_bytes <= 200 * 1024) return launch_scatter<4>(p, block_idx, cu, tiles, col_offsets, rows, heads, slots, g, capacity, st);
+  return launch_scatter<1>(p, block_idx, cu, tiles, col_offsets, rows, heads, slots, g, capacity, st); }
 }
 
 // ---------------------------------------------------------------------------

@@ -27,7 +27,6 @@ def gate_select(q: torch.Tensor, kbar: torch.Tensor, cfg: MoBAConfig, cu_seqlens
         raise ValueError(
             f"representative shape {tuple(kbar.shape)} does not match {prob.num_blocks} blocks")
     out = torch.empty((b, h, s, prob.slots), device=q.device, dtype=torch.int32)
-    lib = _lib.load()
-    _lib.check(lib.moba_b200_gate(prob, _lib.ptr(q), _lib.ptr(kbar), _lib.ptr(cu_seqlens),
-                                  _lib.ptr(out), _lib.stream_ptr(q.device)), "gate_select")
+    _lib.call("moba_b200_gate", q.device, "gate_select", prob, _lib.ptr(q), _lib.ptr(kbar),
+              _lib.ptr(cu_seqlens), _lib.ptr(out))
     return out

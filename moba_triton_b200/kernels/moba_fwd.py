@@ -89,10 +89,8 @@ def attend_partials(q, k, v, cfg: MoBAConfig, index: CSCIndex, causal: bool = Tr
     part_lse, part_o = partials
     prob = _problem(q, k, cfg, index, causal, part_o.dtype == torch.float32 and q.dtype != torch.float32)
     ix = index.c_struct()
-    lib = _lib.load()
-    _lib.check(lib.moba_b200_fwd(prob, _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), ix,
-                                 _lib.ptr(index.cu_seqlens), _lib.ptr(part_o), _lib.ptr(part_lse),
-                                 _lib.stream_ptr(q.device)), "attend_partials")
+    _lib.call("moba_b200_fwd", q.device, "attend_partials", prob, _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), ix,
+              _lib.ptr(index.cu_seqlens), _lib.ptr(part_o), _lib.ptr(part_lse))
     return part_lse, part_o
 
 
@@ -112,9 +110,8 @@ def merge_partials(part_lse, part_o, out_dtype: torch.dtype, return_lse: bool = 
                              part_f32=part_o.dtype == torch.float32 and out_dtype != torch.float32)
     if part_o.dtype not in (out_dtype, torch.float32):
         raise ValueError(f"part_o must be {out_dtype} or float32, got {part_o.dtype}")
-    lib = _lib.load()
-    _lib.check(lib.moba_b200_merge(prob, _lib.ptr(part_o), _lib.ptr(part_lse), _lib.ptr(out),
-                                   _lib.ptr(lse), _lib.stream_ptr(out.device)), "combine_partials")
+    _lib.call("moba_b200_merge", out.device, "combine_partials", prob, _lib.ptr(part_o), _lib.ptr(part_lse),
+              _lib.ptr(out), _lib.ptr(lse))
     return (out, lse) if return_lse else out
 
 

@@ -30,7 +30,5 @@ def pool_blocks(k: torch.Tensor, cfg: MoBAConfig, cu_seqlens=None, max_seqlen=No
     b, s, h, d = k.shape
     prob = _lib.make_problem((b, s, h, d), h, k.dtype, cfg, cu_seqlens, max_seqlen)
     out = torch.empty((n_seq, h, prob.num_blocks, d), device=k.device, dtype=k.dtype)
-    lib = _lib.load()
-    _lib.check(lib.moba_b200_pool(prob, _lib.ptr(k), _lib.ptr(cu_seqlens), _lib.ptr(out),
-                                  _lib.stream_ptr(k.device)), "pool_blocks")
+    _lib.call("moba_b200_pool", k.device, "pool_blocks", prob, _lib.ptr(k), _lib.ptr(cu_seqlens), _lib.ptr(out))
     return out

@@ -77,10 +77,10 @@ def build_csc_from_indices(block_idx: torch.Tensor, num_blocks: int, cfg: MoBACo
     lib = _lib.load()
     nbytes = lib.moba_b200_transpose_scratch_bytes(prob)
     scratch = torch.empty((max(nbytes, 4),), device=dev, dtype=torch.uint8)
-    _lib.check(lib.moba_b200_transpose(
-        prob, _lib.ptr(block_idx), _lib.ptr(cu_seqlens), _lib.ptr(col_nnz), _lib.ptr(col_offsets),
-        _lib.ptr(order), _lib.ptr(row_indices), _lib.ptr(head_indices), _lib.ptr(slot_of_pair),
-        _lib.ptr(scratch), scratch.numel(), _lib.stream_ptr(dev)), "build_csc_from_indices")
+    _lib.call("moba_b200_transpose", dev, "build_csc_from_indices",
+              prob, _lib.ptr(block_idx), _lib.ptr(cu_seqlens), _lib.ptr(col_nnz), _lib.ptr(col_offsets),
+              _lib.ptr(order), _lib.ptr(row_indices), _lib.ptr(head_indices), _lib.ptr(slot_of_pair),
+              _lib.ptr(scratch), scratch.numel())
     return CSCIndex(col_nnz, col_offsets, row_indices, head_indices, slot_of_pair, order,
                     num_blocks=num_blocks, max_slots=slots, num_query_heads=hq,
                     cu_seqlens=cu_seqlens, max_seqlen=max_seqlen)

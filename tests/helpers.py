@@ -31,8 +31,11 @@ def near_tie_report(engine_mask, oracle_mask_, scores, mantissa_bits: int):
     """Classifies every query whose selection differs from the oracle's.
 
     A difference is a *near tie* when the blocks chosen by only one side have
-    scores equal to, or one rounding step away from, those chosen only by the
-    other side. Returns (differing_queries, not_near_tie_queries).
+    scores one rounding step away from those chosen only by the other side: the
+    tensor-core gate rounds a float32 sum, the oracle the exact one. Blocks whose
+    rounded scores are *exactly equal* are not a near tie: for those the rule
+    "ties go to the lower block id" decides, and a swap is a tie-break bug.
+    Returns (differing_queries, not_near_tie_queries).
     """
     em, om = engine_mask.cpu(), oracle_mask_.cpu()
     rows = (em != om).any(dim=-1).nonzero(as_tuple=False)
@@ -44,9 +47,25 @@ def near_tie_report(engine_mask, oracle_mask_, scores, mantissa_bits: int):
             bad += 1
             continue
         step = 2.0 ** (1 - mantissa_bits) * max(float(only_e.abs().max()), float(only_o.abs().max()), 1e-30)
-        if float((only_e.sort().values - only_o.sort().values).abs().max()) > step:
+        gap = (only_e.sort().values - only_o.sort().values).abs()
+        if float(gap.max()) > step or float(gap.min()) == 0.0:
             bad += 1
     return rows.shape[0], bad
+
+
+def assert_on_tensor_core_path(shape, hkv, dtype, cfg, cu=None, max_seqlen=None):
+    """Fails unless the gate, the forward and the backward of this problem run the
+    tcgen05 kernels when the kernel family is left to the library."""
+    from moba_triton_b200 import _lib
+    old = _lib.set_kernel_path(_lib.PATH_AUTO)
+    try:
+        prob = _lib.make_problem(shape, hkv, dtype, cfg, cu, max_seqlen)
+        lib = _lib.load()
+        for stage in (_lib.STAGE_GATE, _lib.STAGE_FWD, _lib.STAGE_BWD):
+            got = lib.moba_b200_path_for(prob, stage)
+            assert got == _lib.PATH_TCGEN05, f"stage {stage} would run kernel family {got}, not tcgen05"
+    finally:
+        _lib.set_kernel_path(old)
 
 
 def oracle_forward(q, k, v, cfg, block_idx, cu=None, causal=True, dout=None, dtype=torch.float64):

@@ -139,3 +139,13 @@ def test_kv_heads_per_pass_arguments_are_checked_before_any_device_work():
             fn(q, k, v, cfg, kv_heads_per_pass=0)
         with pytest.raises(ValueError, match="cannot be combined with index"):
             fn(q, k, v, cfg, index=object(), kv_heads_per_pass=1)
+
+
+def test_a_swapped_exact_tie_is_not_accepted_as_a_near_tie():
+    from helpers import near_tie_report
+    scores = torch.tensor([[[[1.0, 1.0, 0.5, 0.0]]]], dtype=torch.float64)
+    oracle = torch.tensor([[[[True, False, True, False]]]])
+    engine = torch.tensor([[[[False, True, True, False]]]])
+    assert near_tie_report(engine, oracle, scores, 8) == (1, 1)
+    scores[..., 1] = 1.0 - 2.0 ** -8                         # one rounding step apart: a near tie
+    assert near_tie_report(engine, oracle, scores, 8) == (1, 0)

@@ -55,7 +55,15 @@ def test_noalloc_transpose_matches_the_caller_scratch_entry_point(shape, hkv, bs
     cap = (shape[2] // hkv) * (longest or shape[1]) * cfg.slots_per_query
     want = _transpose(False, prob, block_idx, cu_t, hkv, nb, cap, n_seq, device)
     totals = want[0].sum(dim=-1)
+    # another selection of the same shape: run between the compared calls, it leaves foreign
+    # counts in the built-in array, which the next call must not see
+    q2, k2, _ = make_qkv(shape, hkv, dtype=torch.bfloat16, seed=24)
+    other_idx = moba.gate_select(q2.to(device), moba.pool_blocks(k2.to(device), cfg, cu_seqlens=cu_t, max_seqlen=longest),
+                                 cfg, cu_seqlens=cu_t, max_seqlen=longest)
+    assert not torch.equal(other_idx, block_idx)
     for attempt in range(2):                      # two calls in a row share the built-in array
+        if attempt == 1:
+            _transpose(True, prob, other_idx, cu_t, hkv, nb, cap, n_seq, device)
         got = _transpose(True, prob, block_idx, cu_t, hkv, nb, cap, n_seq, device)
         for name, g, w in zip(("col_nnz", "col_offsets", "order"), got[:3], want[:3]):
             assert torch.equal(g, w), f"{name} differs on call {attempt + 1}"
@@ -77,3 +85,31 @@ def test_noalloc_transpose_refuses_problems_beyond_its_built_in_scratch(device):
     rc = lib.moba_b200_transpose_noalloc(prob, p, None, p, p, p, p, p, p, _lib.stream_ptr(device))
     assert rc == -2
     assert b"built-in" in lib.moba_b200_last_error()
+
+
+def test_noalloc_transpose_leaves_device_memory_untouched(device):
+    """The call itself must neither allocate nor free device memory: the free-memory figure
+    of the driver is the same before and after (outputs are allocated beforehand, and the
+    first call, which looks up the built-in array's address, has already happened)."""
+    cfg = moba.MoBAConfig(128, 8)
+    shape, hkv = (1, 4096, 4, 64), 2
+    q, k, _ = make_qkv(shape, hkv, dtype=torch.bfloat16, seed=23)
+    kbar = moba.pool_blocks(k.to(device), cfg)
+    block_idx = moba.gate_select(q.to(device), kbar, cfg)
+    prob = _lib.make_problem(shape, hkv, torch.bfloat16, cfg)
+    nb, cap = kbar.shape[2], (shape[2] // hkv) * shape[1] * cfg.slots_per_query
+    i32 = dict(device=device, dtype=torch.int32)
+    outs = [torch.empty((1, hkv, nb), **i32), torch.empty((1, hkv, nb + 1), **i32), torch.empty((1, hkv, nb), **i32),
+            torch.empty((1, hkv, cap), **i32), torch.empty((1, hkv, cap), **i32), torch.empty((1, hkv, cap), **i32)]
+    lib = _lib.load()
+    args = [prob, _lib.ptr(block_idx), None] + [_lib.ptr(t) for t in outs] + [_lib.stream_ptr(device)]
+    _lib.check(lib.moba_b200_transpose_noalloc(*args), "transpose")      # first call on this device
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(device)
+    reserved_before = torch.cuda.memory_reserved(device)
+    for _ in range(3):
+        _lib.check(lib.moba_b200_transpose_noalloc(*args), "transpose")
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info(device)
+    assert torch.cuda.memory_reserved(device) == reserved_before
+    assert free_after == free_before, "the call changed the amount of free device memory"
