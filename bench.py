@@ -18,6 +18,12 @@ collective runs inside the op. Workloads:
 
 `--impl reference` times the reference algorithm's CPU restatement (oracle/) on
 the host cores for the same workload, on a bounded sample per step.
+
+Every line also carries a `strong` record: the grouped-query and the skewed-load
+configurations with their 8 KV heads sharded over the N GPUs of this run (device-timed,
+max over ranks, per-rank times listed) next to the same whole problem timed on one GPU in
+the same run (rank 0), and the resulting speed-up. `--rows PATH` additionally writes the
+forward measurement as a CSV row in the column layout of the reference's bench driver.
 """
 
 import argparse
@@ -166,6 +172,44 @@ def make_inputs(wl, pinned):
     return out, cu
 
 
+L2_NOTE = "inputs per step (q,k,v,dO >= 268 MB) exceed the 126 MB L2; no flush"
+
+
+def base_config(wl, total_tokens):
+    """The `config` object, identical for both arms of the benchmark."""
+    return {"workload": wl["text"], "tokens_all_gpus": int(total_tokens), "l2": L2_NOTE}
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per (query head, block) pair and launch, from ncu
+# captures of one launch at [1,65536,4,64] (2 082 816 pairs). The traffic of these kernels is
+# per-pair partial rows, so a launch's traffic is this figure times the pairs it processes.
+DRAM_BYTES_PER_PAIR = {
+    "bwd_sm100_kernel": (297.1e6 + 287.1e6) / 2082816,
+    "fwd_sm100_kernel": (172.1e6 + 234.4e6) / 2082816,
+    "gate_sm100_kernel": 33.8e6 / 2082816,
+}
+
+
+def bind_to_gpu_numa_node(gpu_index):
+    """Pins this process to the CPUs NVML reports as local to the GPU, before any pinned
+    buffer is allocated: pinned pages then sit on the GPU's NUMA node and the copy threads
+    run beside them. Reads a property, sets nothing on the GPU. Returns the CPU count or None."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        cpus = {64 * w + b for w, bits in enumerate(mask) for b in range(64) if (bits >> b) & 1}
+        cpus &= set(os.sched_getaffinity(0))
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return len(cpus)
+    except Exception:
+        return None
+    return None
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -180,17 +224,19 @@ def peaks():
 # ----------------------------------------------------------------------------
 
 class ClockSampler:
+    """One nvidia-smi process sampling the given GPUs every 100 ms (rank 0 runs it for the
+    whole job: eight samplers beside eight ranks would compete with the copy threads)."""
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index):
-        self.gpu, self.proc = gpu_index, None
+    def __init__(self, gpu_indices):
+        self.gpus, self.proc = list(gpu_indices), None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}",
+                ["nvidia-smi", "--id=" + ",".join(str(g) for g in self.gpus), f"--query-gpu={self.FIELDS}",
                  "--format=csv,noheader,nounits", "-lms", "100"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
@@ -205,17 +251,21 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             text, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
+        sm, mx, reasons, per_gpu = [], [], set(), {}
         for line in text.splitlines():
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9 or not f[1].isdigit():
                 continue
             sm.append(int(f[1])); mx.append(int(f[2]))
+            per_gpu.setdefault(f[0], []).append(int(f[1]))
             for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        out = {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+               "samples": len(sm), "reasons": sorted(reasons)}
+        if len(per_gpu) > 1:
+            out["sm_mhz_per_gpu"] = {g: statistics.median(v) for g, v in sorted(per_gpu.items())}
+        return out
 
 
 # ----------------------------------------------------------------------------
@@ -254,7 +304,9 @@ def run_reference(args, wl, rank, world):
         "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * secs / args.steps,
         "higher_is_better": True, "scaling": wl["scaling"], "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": {"workload": wl["text"], "sample_per_step": what},
+        "data": "synthetic",
+        "config": base_config(wl, sum(sum(describe(args.workload, r, world)["seqlens"]) for r in range(world))),
+        "sample_per_step": what,
         "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
                          "kind": "port", "sample": what},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -268,6 +320,21 @@ def run_reference(args, wl, rank, world):
 # our arm
 # ----------------------------------------------------------------------------
 
+def device_inputs(wl, dev):
+    """Seeded N(0,1) bf16 q, k, v, dO generated on the device (used by the strong-scaling
+    record only; the headline and end-to-end numbers use host-generated pinned inputs)."""
+    g = torch.Generator(device=dev).manual_seed(77 + wl["seed"])
+    t, hq, hkv, d = sum(wl["seqlens"]), wl["hq"], wl["hkv"], wl["d"]
+    mk = lambda h: torch.randn((1, t, h, d), generator=g, device=dev, dtype=torch.float32)
+    q, k, v, do = mk(hq), mk(hkv), mk(hkv), mk(hq)
+    if wl["skew"]:
+        n = torch.randn((hkv, d), generator=g, device=dev)
+        u = 2.0 * n / n.norm(dim=-1, keepdim=True)
+        q += u.repeat_interleave(hq // hkv, dim=0)[None, None]
+        k[:, : t // 10] += u[None, None]
+    return [x.to(torch.bfloat16) for x in (q, k, v, do)]
+
+
 def run_ours(args, wl, rank, world, local_rank):
     import moba_triton_b200 as moba
     from moba_triton_b200 import _lib
@@ -276,6 +343,7 @@ def run_ours(args, wl, rank, world, local_rank):
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
+    local_cpus = bind_to_gpu_numa_node(local_rank)          # before any pinned allocation
     dist = None
     if world > 1:
         import torch.distributed as dist_mod
@@ -305,7 +373,8 @@ def run_ours(args, wl, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, n):
+    def timed(fn, n, ranks=None):
+        """Device time of n calls of fn, bracketed by barriers: (max over ranks, per-rank list)."""
         barrier()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
@@ -314,27 +383,30 @@ def run_ours(args, wl, rank, world, local_rank):
         b.record()
         barrier()
         ms = a.elapsed_time(b)
-        if dist is not None:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t)
-        return ms
+        if dist is None:
+            return ms, [ms]
+        mine = torch.tensor([ms], device=dev)
+        every = torch.empty(world, device=dev)
+        dist.all_gather_into_tensor(every, mine)
+        return float(every.max()), [float(x) for x in every.tolist()]
 
     # nvidia-smi needs a few hundred ms to deliver its first sample, so the sampler runs from
     # the warm-up on, and the same step keeps running (untimed) after the timed region until
     # the sampler has had about a second under this load.
-    clocks = ClockSampler(local_rank)
-    clocks.start()
+    clocks = ClockSampler(range(world)) if rank == 0 else None
+    if clocks is not None:
+        clocks.start()
     t_load = time.perf_counter()
     for _ in range(args.warmup):
         step()
     launches0 = _lib.launch_count()
-    ms_total = timed(step, args.steps)
+    ms_total, per_rank_total = timed(step, args.steps)
     launches = _lib.launch_count() - launches0
     while time.perf_counter() - t_load < 1.2:
         step()
     torch.cuda.synchronize()
-    clock_info = clocks.stop()
+    barrier()
+    clock_info = clocks.stop() if clocks is not None else None
     ms_step = ms_total / args.steps
 
     # forward only (inference entry point)
@@ -342,7 +414,10 @@ def run_ours(args, wl, rank, world, local_rank):
         fwd = lambda: moba.moba_forward(q, k, v, cfg, **kw)
         for _ in range(2):
             fwd()
-        ms_fwd = timed(fwd, max(2, args.steps // 2)) / max(2, args.steps // 2)
+        torch.cuda.reset_peak_memory_stats(dev)
+        n_fwd = max(2, args.steps // 2)
+        ms_fwd = timed(fwd, n_fwd)[0] / n_fwd
+        fwd_peak_mb = torch.cuda.max_memory_allocated(dev) / (1 << 20)
 
     # end to end: host buffers in, host buffers out, through the public API. Every step copies
     # its q, k, v, dO from pinned host memory and its O, dQ, dK, dV back. The copies run on two
@@ -385,12 +460,28 @@ def run_ours(args, wl, rank, world, local_rank):
 
     e2e_steps = max(2, min(args.steps, 5))
     e2e_run(1)
-    ms_e2e = timed(lambda: e2e_run(e2e_steps), 1) / e2e_steps
+    ms_e2e_total, per_rank_e2e = timed(lambda: e2e_run(e2e_steps), 1)
+    ms_e2e = ms_e2e_total / e2e_steps
     # the overlapped path must deliver what the plain call computes (the op is deterministic)
     e2e_ok = bool(torch.equal(outs_host[0], step().detach().cpu()) and
                   torch.equal(outs_host[1], q.grad.cpu()))
     h2d = sum(h.numel() * h.element_size() for h in host)
     d2h = sum(h.numel() * h.element_size() for h in outs_host)
+    # the copies alone, one direction at a time: what the host side of the step can deliver
+    dev_in = [torch.empty_like(h, device=dev) for h in host]
+    dev_out = [torch.empty_like(h, device=dev) for h in outs_host]
+
+    def h2d_only():
+        for d_, h_ in zip(dev_in, host):
+            d_.copy_(h_, non_blocking=True)
+
+    def d2h_only():
+        for h_, d_ in zip(outs_host, dev_out):
+            h_.copy_(d_, non_blocking=True)
+
+    ms_h2d, per_rank_h2d = timed(h2d_only, 3)
+    ms_d2h, per_rank_d2h = timed(d2h_only, 3)
+    del dev_in, dev_out
 
     # per-kernel durations (CUDA events on the launching stream, inside the library)
     _lib.profile(True)
@@ -409,6 +500,48 @@ def run_ours(args, wl, rank, world, local_rank):
         total_f, total_tokens = float(t[0]), int(t[1])
     pk = peaks()
 
+    # ---- strong scaling of the sharded configurations, on every line ----
+    del q, k, v, do
+    torch.cuda.empty_cache()
+
+    def strong_case(name):
+        if 8 % world:
+            return {"workload": name, "skipped": f"8 KV heads do not shard over {world} GPUs"}
+        def run(swl, active):
+            if not active:
+                return None
+            qq, kk, vv, dd = device_inputs(swl, dev)
+            qq.requires_grad_(True); kk.requires_grad_(True); vv.requires_grad_(True)
+            def one():
+                qq.grad = kk.grad = vv.grad = None
+                moba.moba_attention(qq, kk, vv, cfg).backward(dd)
+            return one
+        sharded = run(describe(name, rank, world), True)
+        for _ in range(2):
+            sharded()
+        ms, per_rank = timed(sharded, 3)
+        del sharded
+        torch.cuda.empty_cache()
+        rec = {"workload": describe(name, 0, world)["text"], "n_gpus": world, "ms_sharded": ms / 3,
+               "per_rank_ms": [x / 3 for x in per_rank], "inputs": "seeded N(0,1), generated on the device"}
+        if world == 1:
+            rec["ms_one_gpu"], rec["speedup"] = rec["ms_sharded"], 1.0
+            return rec
+        whole = run(describe(name, 0, 1), rank == 0)           # rank 0 alone times the whole problem
+        if whole is not None:
+            for _ in range(2):
+                whole()
+        ms_one, _ = timed((whole if whole is not None else (lambda: None)), 3)
+        one = torch.tensor([ms_one / 3 if rank == 0 else 0.0], device=dev)
+        dist.all_reduce(one, op=dist.ReduceOp.MAX)
+        del whole
+        torch.cuda.empty_cache()
+        rec["ms_one_gpu"] = float(one)
+        rec["speedup"] = rec["ms_one_gpu"] / rec["ms_sharded"]
+        return rec
+
+    strong = [] if args.no_strong else [strong_case("gqa"), strong_case("skewed")]
+
     if rank == 0:
         kernels = {n: {"launches_per_step": c / prof_steps, "ms_per_launch": ms / c,
                        "share": ms / max(1e-9, sum(m for _, m in table.values()))}
@@ -420,39 +553,49 @@ def run_ours(args, wl, rank, world, local_rank):
             achieved, peak, unit = amount / dur_s / 1e12, pk["tensor"], "TFLOP/s"
         else:
             achieved, peak, unit = amount / dur_s / 1e9, pk["hbm"], "GB/s"
-        # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised in
-        # profiles/tensor_kernels_cfg2_ncu_full.md: measured at 2 082 816 (query head, block) pairs
-        # and scaled by this run's pair count (the traffic is per-pair partial rows).
-        per_pair = {"bwd_sm100_kernel": (297.1e6 + 287.1e6) / 2082816, "fwd_sm100_kernel": (172.7e6 + 234.6e6) / 2082816,
-                    "gate_sm100_kernel": 33.8e6 / 2082816}
-        traffic = per_pair[top] * acct["pairs"] if top in per_pair else None
+        traffic = DRAM_BYTES_PER_PAIR[top] * acct["pairs"] if top in DRAM_BYTES_PER_PAIR else None
         t_roof = max(acct["f_step"] / (pk["tensor_burst"] * 1e12), acct["bytes_step"] / (pk["hbm"] * 1e9))
+        roofline = {"kernel": top, "bound": kind, "achieved": achieved, "peak": peak, "unit": unit,
+                    "frac": achieved / peak, "traffic": traffic,
+                    "peak_source": f"{pk['source']} ({'sustained' if kind == 'tensor' else 'copy'})"}
+        if kind == "tensor":
+            roofline["frac_burst"] = achieved / pk["tensor_burst"]
+            roofline["peak_burst"] = pk["tensor_burst"]
+        config = base_config(wl, total_tokens)
         line = {
             "metric": METRIC, "value": total_f / (ms_step * 1e-3) / 1e12, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "per_rank_ms_per_step": [x / args.steps for x in per_rank_total],
             "higher_is_better": True, "scaling": wl["scaling"],
             "vs_baseline": (H100_REFERENCE_FWD_BWD_MS / ms_step) if wl["name"] == "target" else None,
             "vs_baseline_note": "reference Triton kernels on H100, fwd+bwd at [1,131072,4,64]: 6.181 ms; "
                                 "the reference publishes no B200 number",
-            "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": wl["text"], "l2": "inputs per step (q,k,v,dO >= 268 MB) exceed the 126 MB L2; no flush",
-                       "tokens_all_gpus": total_tokens, "kernel_path": args.path or "auto"},
+            "dtype": "bf16", "data": "synthetic", "config": config, "kernel_path": args.path or "auto",
             "fwd_ms": ms_fwd, "fwd_tflops": acct["f_fwd"] / (ms_fwd * 1e-3) / 1e12,
             "op_roofline": {"t_roof_ms": t_roof * 1e3, "frac": t_roof * 1e3 / ms_step,
                             "peak": f"{pk['tensor_burst']} TFLOP/s burst, {pk['hbm']} GB/s ({pk['source']})"},
-            "e2e": {"value": total_f / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e, "outputs_match_resident_run": e2e_ok,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "e2e": {"value": total_f / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+                    "per_rank_ms_per_step": [x / e2e_steps for x in per_rank_e2e],
+                    "outputs_match_resident_run": e2e_ok,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "h2d_only_ms": ms_h2d / 3, "d2h_only_ms": ms_d2h / 3,
+                    "per_rank_h2d_only_ms": [x / 3 for x in per_rank_h2d],
+                    "per_rank_d2h_only_ms": [x / 3 for x in per_rank_d2h],
+                    "cpus_bound_to_gpu_numa_node": local_cpus},
             "gpu_launches": launches,
             "clocks": clock_info,
-            "roofline": {"kernel": top, "bound": kind, "achieved": achieved, "peak": peak, "unit": unit,
-                         "frac": achieved / peak, "traffic": traffic,
-                         "peak_source": f"{pk['source']} ({'sustained' if kind == 'tensor' else 'copy'})"},
+            "roofline": roofline,
             "kernels": kernels,
+            "strong": strong,
         }
         if world == 1 and not args.no_cpu_baseline:
             f, dt, what = cpu_sample(wl, 65536)
             line["cpu_baseline"] = {"value": f / dt / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
                                     "kind": "port", "sample": what, "seconds": dt}
+        if args.rows and not wl["packed"]:
+            from moba_triton_b200 import bench_rows
+            shape = (1, sum(wl["seqlens"]), wl["hq"], wl["d"])
+            bench_rows.write_csv(args.rows, [bench_rows.make_row("ours_b200", shape, cfg, ms_fwd, fwd_peak_mb, device=dev)])
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
@@ -468,6 +611,8 @@ def main():
     ap.add_argument("--workload", default="target")
     ap.add_argument("--path", default="", choices=["", "portable", "tcgen05"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-strong", action="store_true", help="skip the strong-scaling record")
+    ap.add_argument("--rows", default="", help="write the forward measurement as a CSV row here")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))

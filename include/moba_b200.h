@@ -20,6 +20,7 @@
  *   col_offsets           [n_seq, Hkv, num_blocks+1] int32
  *   row/head/slot arrays  [n_seq, Hkv, capacity]     int32,
  *                         capacity = (Hq/Hkv) * max_seqlen * slots
+ *   work_items            [n_seq, Hkv, items_per_row, 4]  int32
  *   part_o                [B, Hq, S, slots, D]  (dtype of q, or float32)
  *   part_lse, dq marker   [B, Hq, S, slots]     float32, log2 units, -inf = unwritten
  *   lse, delta            [B, Hq, S]            float32 (lse in log2 units)
@@ -35,7 +36,7 @@
 extern "C" {
 #endif
 
-#define MOBA_B200_ABI_VERSION 1
+#define MOBA_B200_ABI_VERSION 2
 
 enum { MOBA_B200_F32 = 0, MOBA_B200_BF16 = 1, MOBA_B200_F16 = 2 };
 
@@ -72,6 +73,8 @@ typedef struct moba_b200_problem {
   int32_t packed;         /* 1: cu_seqlens describes the token axis */
   int32_t path;           /* MOBA_B200_PATH_* */
   int32_t part_f32;       /* 1: part_o is float32 instead of the dtype of q */
+  int32_t chunk_tiles;    /* scheduling: a column is dispatched in work items of at most this many
+                             128-query tiles; 0 = the library's policy (moba_b200_chunk_tiles) */
 } moba_b200_problem;
 
 typedef struct moba_b200_index {
@@ -82,6 +85,11 @@ typedef struct moba_b200_index {
   const int32_t* head_indices;
   const int32_t* slot_of_pair;
   int64_t capacity;       /* entries per (sequence, kv head) in the three pair arrays */
+  const int32_t* work_items; /* [n_seq, Hkv, items_per_row, 4]: {block, first tile, tiles, dK/dV partial
+                                slot or -1 (whole column) or -2 (padding)}, in dispatch order; written
+                                by moba_b200_transpose. NULL: the tensor-core kernels refuse the index */
+  int32_t items_per_row;  /* moba_b200_work_items_per_row() of the problem the index was built for */
+  int32_t chunk_tiles;    /* the chunk size the items were cut with */
 } moba_b200_index;
 
 /* ABI version of the loaded library (compare with MOBA_B200_ABI_VERSION). */
@@ -117,6 +125,23 @@ int moba_b200_path_for(const moba_b200_problem* p, int stage);
 /* Bytes of scratch moba_b200_transpose needs for this problem. */
 size_t moba_b200_transpose_scratch_bytes(const moba_b200_problem* p);
 
+/* Scheduling. The persistent tensor-core kernels do not dispatch whole columns: the
+ * transpose cuts every (sequence, kv head, block) column, in longest-first order, into
+ * work items of at most chunk_tiles tiles of 128 queries, so that a few crowded
+ * columns (the early blocks of a causal sequence, or a skewed selection) cannot hold
+ * the last SMs busy while the others idle. The forward treats each item as a column
+ * of its own; in the backward the items of a split column write float32 dK/dV
+ * partials into `dkv_scratch`, summed in item order by a reduction pass.
+ *   moba_b200_chunk_tiles         the chunk size used for this problem (the policy:
+ *                                 total tiles / (4 x 148 SMs), at least 8; or p->chunk_tiles)
+ *   moba_b200_work_items_per_row  entries per (sequence, kv head) of index.work_items
+ *   moba_b200_dkv_scratch_bytes   bytes of dkv_scratch moba_b200_bwd needs
+ * The reference orders blocks longest first and leaves the rest to the hardware
+ * scheduler (src/moba/kernels/routing.py:188-247); it has no counterpart of the split. */
+int moba_b200_chunk_tiles(const moba_b200_problem* p);
+int moba_b200_work_items_per_row(const moba_b200_problem* p);
+size_t moba_b200_dkv_scratch_bytes(const moba_b200_problem* p);
+
 /* Mean key of every block.
  * Replaces pool_blocks / pool_blocks_kernel (src/moba/kernels/pooling.py:25-163). */
 int moba_b200_pool(const moba_b200_problem* p, const void* k, const int32_t* cu_seqlens,
@@ -135,8 +160,8 @@ int moba_b200_gate(const moba_b200_problem* p, const void* q, const void* kbar,
 int moba_b200_transpose(const moba_b200_problem* p, const int32_t* block_idx,
                         const int32_t* cu_seqlens, int32_t* col_nnz, int32_t* col_offsets,
                         int32_t* order, int32_t* row_indices, int32_t* head_indices,
-                        int32_t* slot_of_pair, void* scratch, size_t scratch_bytes,
-                        void* stream);
+                        int32_t* slot_of_pair, int32_t* work_items, void* scratch,
+                        size_t scratch_bytes, void* stream);
 
 /* moba_b200_transpose for callers that cannot allocate device memory -- a
  * server that fixes its whole memory plan at start-up and forbids cudaMalloc
@@ -155,7 +180,7 @@ int moba_b200_transpose(const moba_b200_problem* p, const int32_t* block_idx,
 int moba_b200_transpose_noalloc(const moba_b200_problem* p, const int32_t* block_idx,
                                 const int32_t* cu_seqlens, int32_t* col_nnz, int32_t* col_offsets,
                                 int32_t* order, int32_t* row_indices, int32_t* head_indices,
-                                int32_t* slot_of_pair, void* stream);
+                                int32_t* slot_of_pair, int32_t* work_items, void* stream);
 
 /* KV-block-major attention: one K/V block resident per CTA, the queries that
  * selected it gathered through the index; writes normalised partial outputs and
@@ -173,14 +198,44 @@ int moba_b200_merge(const moba_b200_problem* p, const void* part_o, const float*
                     void* out, float* lse, void* stream);
 
 /* Backward: delta = rowsum(out*dout); per KV block dK/dV owned by one CTA and
- * stored once (zeros for unselected blocks); dQ written as per-(query, slot)
- * partials and summed in slot order. `part_lse` is the forward's buffer, used
- * as the written-slot marker. Replaces compute_delta, moba_backward /
- * moba_bwd_kernel and reduce_dq (src/moba/kernels/moba_bwd.py:134-160,215-579). */
+ * stored once (zeros for unselected blocks) -- or, for a column cut into several
+ * work items, accumulated per item in `dkv_scratch` (moba_b200_dkv_scratch_bytes)
+ * and summed in item order; dQ written as per-(query, slot) partials and summed in
+ * slot order. `part_lse` is the forward's buffer, used as the written-slot marker.
+ * Replaces compute_delta, moba_backward / moba_bwd_kernel and reduce_dq
+ * (src/moba/kernels/moba_bwd.py:134-160,215-579). */
 int moba_b200_bwd(const moba_b200_problem* p, const void* q, const void* k, const void* v,
                   const void* out, const void* dout, const float* lse, const float* part_lse,
                   const moba_b200_index* index, const int32_t* cu_seqlens,
-                  float* delta, void* dq_part, void* dq, void* dk, void* dv, void* stream);
+                  float* delta, void* dq_part, void* dkv_scratch, void* dq, void* dk, void* dv,
+                  void* stream);
+
+/* Packed (variable-length) batches, the step either side of the op. A "row" is
+ * one token's H*D elements (row_bytes, a multiple of 16), contiguous in the
+ * token-major layout.
+ *
+ * moba_b200_pack_index scans a [batch, seq_len] mask (elements of 1, 4 or 8
+ * bytes, nonzero = keep): dest[b, s] = position of token s among the kept tokens
+ * of row b, or -1; lengths[b]; cu_seqlens[batch + 1]; meta = {total kept tokens,
+ * longest row}, which the host reads once to size the packed buffer.
+ * moba_b200_pack_rows then copies the kept rows of x [batch, seq_len, row] to
+ * packed [total, row] in (b, s) order.
+ * Replace pack (src/moba/varlen.py:114-156). */
+int moba_b200_pack_index(const void* mask, int mask_elem_bytes, int batch, int seq_len,
+                         int32_t* dest, int32_t* lengths, int32_t* cu_seqlens, int32_t* meta,
+                         void* stream);
+int moba_b200_pack_rows(const void* x, const int32_t* dest, const int32_t* cu_seqlens,
+                        void* packed, int batch, int seq_len, size_t row_bytes, void* stream);
+
+/* Inverse: out [batch, seq_len, row] takes row cu_seqlens[b] + s of packed where
+ * s is inside sequence b and zeros elsewhere.
+ * Replaces unpack (src/moba/varlen.py:159-205). */
+int moba_b200_unpack_rows(const void* packed, const int32_t* cu_seqlens, void* out, int batch,
+                          int seq_len, size_t row_bytes, void* stream);
+
+/* meta = {cu_seqlens[n_seq], longest sequence} of an existing cu_seqlens; what
+ * from_nested (src/moba/varlen.py:208-236) reads back to report max_seqlen. */
+int moba_b200_seq_meta(const int32_t* cu_seqlens, int n_seq, int32_t* meta, void* stream);
 
 #ifdef __cplusplus
 }

@@ -16,7 +16,7 @@ LIB_PATH = os.environ.get("MOBA_B200_LIBRARY", os.path.join(PKG, "libmoba_b200.s
 F32, BF16, F16 = 0, 1, 2
 PATH_AUTO, PATH_PORTABLE, PATH_TCGEN05 = 0, 1, 2
 STAGE_GATE, STAGE_FWD, STAGE_BWD = 0, 1, 2
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 _DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
 
@@ -26,6 +26,8 @@ EXPORTS = (
     "moba_b200_transpose", "moba_b200_fwd", "moba_b200_merge", "moba_b200_bwd",
     "moba_b200_launch_count", "moba_b200_profile_enable", "moba_b200_profile_read",
     "moba_b200_device_status", "moba_b200_transpose_noalloc",
+    "moba_b200_pack_index", "moba_b200_pack_rows", "moba_b200_unpack_rows", "moba_b200_seq_meta",
+    "moba_b200_chunk_tiles", "moba_b200_work_items_per_row", "moba_b200_dkv_scratch_bytes",
 )
 
 
@@ -33,13 +35,14 @@ class Problem(Structure):
     _fields_ = [(n, c_int32) for n in (
         "dtype", "batch", "tokens", "n_seq", "max_seqlen", "q_heads", "kv_heads", "head_dim",
         "block_size", "top_k", "slots", "take", "always_current", "num_blocks", "causal",
-        "packed", "path", "part_f32")]
+        "packed", "path", "part_f32", "chunk_tiles")]
 
 
 class Index(Structure):
     _fields_ = [("col_nnz", c_void_p), ("col_offsets", c_void_p), ("order", c_void_p),
                 ("row_indices", c_void_p), ("head_indices", c_void_p),
-                ("slot_of_pair", c_void_p), ("capacity", c_int64)]
+                ("slot_of_pair", c_void_p), ("capacity", c_int64),
+                ("work_items", c_void_p), ("items_per_row", c_int32), ("chunk_tiles", c_int32)]
 
 
 _lib = None
@@ -63,11 +66,19 @@ def load():
     lib.moba_b200_transpose_scratch_bytes.restype = c_size_t
     lib.moba_b200_pool.argtypes = [P, vp, vp, vp, vp]
     lib.moba_b200_gate.argtypes = [P, vp, vp, vp, vp, vp]
-    lib.moba_b200_transpose.argtypes = [P, vp, vp, vp, vp, vp, vp, vp, vp, vp, c_size_t, vp]
-    lib.moba_b200_transpose_noalloc.argtypes = [P, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+    lib.moba_b200_transpose.argtypes = [P, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, c_size_t, vp]
+    lib.moba_b200_transpose_noalloc.argtypes = [P, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+    lib.moba_b200_chunk_tiles.argtypes = [P]
+    lib.moba_b200_work_items_per_row.argtypes = [P]
+    lib.moba_b200_dkv_scratch_bytes.argtypes = [P]
+    lib.moba_b200_dkv_scratch_bytes.restype = c_size_t
     lib.moba_b200_fwd.argtypes = [P, vp, vp, vp, I, vp, vp, vp, vp]
     lib.moba_b200_merge.argtypes = [P, vp, vp, vp, vp, vp]
-    lib.moba_b200_bwd.argtypes = [P, vp, vp, vp, vp, vp, vp, vp, I, vp, vp, vp, vp, vp, vp, vp]
+    lib.moba_b200_bwd.argtypes = [P, vp, vp, vp, vp, vp, vp, vp, I, vp, vp, vp, vp, vp, vp, vp, vp]
+    lib.moba_b200_pack_index.argtypes = [vp, c_int, c_int, c_int, vp, vp, vp, vp, vp]
+    lib.moba_b200_pack_rows.argtypes = [vp, vp, vp, vp, c_int, c_int, c_size_t, vp]
+    lib.moba_b200_unpack_rows.argtypes = [vp, vp, vp, c_int, c_int, c_size_t, vp]
+    lib.moba_b200_seq_meta.argtypes = [vp, c_int, vp, vp]
     lib.moba_b200_device_status.argtypes = [POINTER(ctypes.c_uint), vp]
     lib.moba_b200_launch_count.restype = ctypes.c_longlong
     lib.moba_b200_profile_enable.argtypes = [c_int]
@@ -153,6 +164,16 @@ def require_cuda(*tensors) -> None:
 
 
 _force_path = [PATH_AUTO]
+_chunk_tiles = [0]
+
+
+def set_chunk_tiles(tiles: int) -> int:
+    """Overrides the scheduling chunk size (work items of at most `tiles` 128-query tiles;
+    0 = the library's policy) for indices built from now on; returns the previous setting.
+    Meant for tests: a small value makes small problems take the split-column paths."""
+    old = _chunk_tiles[0]
+    _chunk_tiles[0] = int(tiles)
+    return old
 
 
 def set_kernel_path(path: int) -> int:
@@ -164,7 +185,8 @@ def set_kernel_path(path: int) -> int:
 
 
 def make_problem(q_shape, kv_heads: int, dtype: torch.dtype, cfg, cu_seqlens=None,
-                 max_seqlen=None, causal: bool = True, part_f32: bool = False) -> Problem:
+                 max_seqlen=None, causal: bool = True, part_f32: bool = False,
+                 chunk_tiles=None) -> Problem:
     b, s, hq, d = q_shape
     packed = cu_seqlens is not None
     n_seq = cu_seqlens.numel() - 1 if packed else b
@@ -175,4 +197,5 @@ def make_problem(q_shape, kv_heads: int, dtype: torch.dtype, cfg, cu_seqlens=Non
         q_heads=hq, kv_heads=kv_heads, head_dim=d, block_size=cfg.block_size, top_k=cfg.top_k,
         slots=cfg.slots_per_query, take=cfg.past_blocks_selected(nb),
         always_current=int(cfg.always_select_current), num_blocks=nb, causal=int(causal),
-        packed=int(packed), path=_force_path[0], part_f32=int(part_f32))
+        packed=int(packed), path=_force_path[0], part_f32=int(part_f32),
+        chunk_tiles=_chunk_tiles[0] if chunk_tiles is None else int(chunk_tiles))

@@ -81,6 +81,7 @@ static int check_problem(const moba_b200_problem* p) {
     set_error("num_blocks %d does not match max_seqlen %d / block_size %d", p->num_blocks, p->max_seqlen, p->block_size);
     return MOBA_B200_EINVAL;
   }
+  if (p->chunk_tiles < 0) { set_error("chunk_tiles must not be negative"); return MOBA_B200_EINVAL; }
   if ((long long)(p->q_heads / p->kv_heads) * p->max_seqlen * p->slots > 0x7fffffffLL) {
     set_error("a (sequence, kv head) column list would exceed 2^31 entries"); return MOBA_B200_EUNSUPPORTED;
   }
@@ -174,6 +175,23 @@ size_t moba_b200_transpose_scratch_bytes(const moba_b200_problem* p) {
   return transpose_scratch_bytes(*p);
 }
 
+int moba_b200_chunk_tiles(const moba_b200_problem* p) {
+  MOBA_TRY(check_problem(p));
+  return sched_chunk_tiles(*p);
+}
+
+int moba_b200_work_items_per_row(const moba_b200_problem* p) {
+  MOBA_TRY(check_problem(p));
+  const long long n = sched_items_per_row(*p);
+  if (n > 0x7fffffffLL) { set_error("chunk_tiles %d cuts the problem into too many work items", sched_chunk_tiles(*p)); return MOBA_B200_EUNSUPPORTED; }
+  return (int)n;
+}
+
+size_t moba_b200_dkv_scratch_bytes(const moba_b200_problem* p) {
+  if (check_problem(p) != MOBA_B200_OK) return 0;
+  return sched_dkv_scratch_bytes(*p);
+}
+
 int moba_b200_pool(const moba_b200_problem* p, const void* k, const int32_t* cu_seqlens,
                    void* kbar, void* stream) {
   MOBA_TRY(check_problem(p));
@@ -197,29 +215,31 @@ int moba_b200_gate(const moba_b200_problem* p, const void* q, const void* kbar,
 int moba_b200_transpose(const moba_b200_problem* p, const int32_t* block_idx,
                         const int32_t* cu_seqlens, int32_t* col_nnz, int32_t* col_offsets,
                         int32_t* order, int32_t* row_indices, int32_t* head_indices,
-                        int32_t* slot_of_pair, void* scratch, size_t scratch_bytes, void* stream) {
+                        int32_t* slot_of_pair, int32_t* work_items, void* scratch, size_t scratch_bytes,
+                        void* stream) {
   MOBA_TRY(check_problem(p));
   MOBA_TRY(need(block_idx, "block_idx")); MOBA_TRY(need(col_nnz, "col_nnz"));
   MOBA_TRY(need(col_offsets, "col_offsets")); MOBA_TRY(need(order, "order"));
   MOBA_TRY(need(row_indices, "row_indices")); MOBA_TRY(need(head_indices, "head_indices"));
-  MOBA_TRY(need(slot_of_pair, "slot_of_pair")); MOBA_TRY(need(scratch, "scratch"));
+  MOBA_TRY(need(slot_of_pair, "slot_of_pair")); MOBA_TRY(need(work_items, "work_items"));
+  MOBA_TRY(need(scratch, "scratch"));
   if (p->packed) MOBA_TRY(need(cu_seqlens, "cu_seqlens"));
   return launch_transpose(*p, block_idx, cu_seqlens, col_nnz, col_offsets, order, row_indices,
-                          head_indices, slot_of_pair, scratch, scratch_bytes, (cudaStream_t)stream);
+                          head_indices, slot_of_pair, work_items, scratch, scratch_bytes, (cudaStream_t)stream);
 }
 
 int moba_b200_transpose_noalloc(const moba_b200_problem* p, const int32_t* block_idx,
                                 const int32_t* cu_seqlens, int32_t* col_nnz, int32_t* col_offsets,
                                 int32_t* order, int32_t* row_indices, int32_t* head_indices,
-                                int32_t* slot_of_pair, void* stream) {
+                                int32_t* slot_of_pair, int32_t* work_items, void* stream) {
   MOBA_TRY(check_problem(p));
   MOBA_TRY(need(block_idx, "block_idx")); MOBA_TRY(need(col_nnz, "col_nnz"));
   MOBA_TRY(need(col_offsets, "col_offsets")); MOBA_TRY(need(order, "order"));
   MOBA_TRY(need(row_indices, "row_indices")); MOBA_TRY(need(head_indices, "head_indices"));
-  MOBA_TRY(need(slot_of_pair, "slot_of_pair"));
+  MOBA_TRY(need(slot_of_pair, "slot_of_pair")); MOBA_TRY(need(work_items, "work_items"));
   if (p->packed) MOBA_TRY(need(cu_seqlens, "cu_seqlens"));
   return launch_transpose_noalloc(*p, block_idx, cu_seqlens, col_nnz, col_offsets, order, row_indices,
-                                  head_indices, slot_of_pair, (cudaStream_t)stream);
+                                  head_indices, slot_of_pair, work_items, (cudaStream_t)stream);
 }
 
 static int check_index(const moba_b200_problem* p, const moba_b200_index* ix) {
@@ -228,7 +248,12 @@ static int check_index(const moba_b200_problem* p, const moba_b200_index* ix) {
   MOBA_TRY(need(ix->order, "index.order")); MOBA_TRY(need(ix->row_indices, "index.row_indices"));
   MOBA_TRY(need(ix->head_indices, "index.head_indices")); MOBA_TRY(need(ix->slot_of_pair, "index.slot_of_pair"));
   if (ix->capacity <= 0) { set_error("index.capacity must be positive"); return MOBA_B200_EINVAL; }
-  (void)p;
+  if (ix->work_items != nullptr &&
+      (ix->items_per_row != sched_items_per_row(*p) || ix->chunk_tiles != sched_chunk_tiles(*p))) {
+    set_error("index.work_items was cut for another problem (items_per_row %d, chunk_tiles %d; this call: %lld, %d)",
+              ix->items_per_row, ix->chunk_tiles, sched_items_per_row(*p), sched_chunk_tiles(*p));
+    return MOBA_B200_EINVAL;
+  }
   return MOBA_B200_OK;
 }
 
@@ -259,7 +284,7 @@ int moba_b200_merge(const moba_b200_problem* p, const void* part_o, const float*
 int moba_b200_bwd(const moba_b200_problem* p, const void* q, const void* k, const void* v,
                   const void* out, const void* dout, const float* lse, const float* part_lse,
                   const moba_b200_index* index, const int32_t* cu_seqlens, float* delta,
-                  void* dq_part, void* dq, void* dk, void* dv, void* stream) {
+                  void* dq_part, void* dkv_scratch, void* dq, void* dk, void* dv, void* stream) {
   MOBA_TRY(check_problem(p));
   MOBA_TRY(check_index(p, index));
   MOBA_TRY(need(q, "q")); MOBA_TRY(need(k, "k")); MOBA_TRY(need(v, "v"));
@@ -272,10 +297,38 @@ int moba_b200_bwd(const moba_b200_problem* p, const void* q, const void* k, cons
   cudaStream_t st = (cudaStream_t)stream;
   MOBA_TRY(launch_delta(*p, out, dout, delta, st));
   if (path == MOBA_B200_PATH_TCGEN05)
-    MOBA_TRY(launch_bwd_sm100(*p, q, k, v, dout, lse, delta, *index, cu_seqlens, dq_part, dk, dv, st));
+    MOBA_TRY(launch_bwd_sm100(*p, q, k, v, dout, lse, delta, *index, cu_seqlens, dq_part,
+                              static_cast<float*>(dkv_scratch), dk, dv, st));
   else
     MOBA_TRY(launch_bwd_portable(*p, q, k, v, dout, lse, delta, *index, cu_seqlens, dq_part, dk, dv, st));
   return launch_dq_reduce(*p, dq_part, part_lse, dq, st);
+}
+
+int moba_b200_pack_index(const void* mask, int mask_elem_bytes, int batch, int seq_len, int32_t* dest,
+                         int32_t* lengths, int32_t* cu_seqlens, int32_t* meta, void* stream) {
+  MOBA_TRY(need(mask, "mask")); MOBA_TRY(need(dest, "dest")); MOBA_TRY(need(lengths, "lengths"));
+  MOBA_TRY(need(cu_seqlens, "cu_seqlens")); MOBA_TRY(need(meta, "meta"));
+  if (batch <= 0 || seq_len <= 0) { set_error("pack: batch and seq_len must be positive"); return MOBA_B200_EINVAL; }
+  return launch_pack_index(mask, mask_elem_bytes, batch, seq_len, dest, lengths, cu_seqlens, meta, (cudaStream_t)stream);
+}
+
+int moba_b200_pack_rows(const void* x, const int32_t* dest, const int32_t* cu_seqlens, void* packed, int batch,
+                        int seq_len, size_t row_bytes, void* stream) {
+  MOBA_TRY(need(x, "x")); MOBA_TRY(need(dest, "dest")); MOBA_TRY(need(cu_seqlens, "cu_seqlens"));
+  MOBA_TRY(need(packed, "packed"));
+  return launch_pack_rows(x, dest, cu_seqlens, packed, batch, seq_len, row_bytes, (cudaStream_t)stream);
+}
+
+int moba_b200_unpack_rows(const void* packed, const int32_t* cu_seqlens, void* out, int batch, int seq_len,
+                          size_t row_bytes, void* stream) {
+  MOBA_TRY(need(packed, "packed")); MOBA_TRY(need(cu_seqlens, "cu_seqlens")); MOBA_TRY(need(out, "out"));
+  return launch_unpack_rows(packed, cu_seqlens, out, batch, seq_len, row_bytes, (cudaStream_t)stream);
+}
+
+int moba_b200_seq_meta(const int32_t* cu_seqlens, int n_seq, int32_t* meta, void* stream) {
+  MOBA_TRY(need(cu_seqlens, "cu_seqlens")); MOBA_TRY(need(meta, "meta"));
+  if (n_seq <= 0) { set_error("seq_meta: n_seq must be positive"); return MOBA_B200_EINVAL; }
+  return launch_seq_meta(cu_seqlens, n_seq, meta, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -246,7 +246,7 @@ merge_kernel(const TP* __restrict__ part_o, const float* __restrict__ part_lse,
     for (int u = 0; u < kAhead; ++u) li[u] = (i0 + u < slots) ? ls[i0 + u] : -INFINITY;
 #pragma unroll
     for (int u = 0; u < kAhead; ++u)                           // unwritten: never touch its data
-      raw[u] = (li[u] > -INFINITY) ? *reinterpret_cast<const uint4*>(po + (size_t)(i0 + u) * d) : make_uint4(0, 0, 0, 0);
+      raw[u] = (li[u] > -INFINITY) ? __ldcs(reinterpret_cast<const uint4*>(po + (size_t)(i0 + u) * d)) : make_uint4(0, 0, 0, 0);
 #pragma unroll
     for (int u = 0; u < kAhead; ++u) {
       if (!(li[u] > -INFINITY)) continue;

@@ -10,8 +10,10 @@
 //   loader   (1 warp)    walks the work list, publishes each column's descriptor in
 //                        shared memory, TMA-loads its K block and V block; zeroes the
 //                        rows of a block that its sequence cuts short
-//   mma      (1 thread)  S = Q K^T (M128 N128 K=D), then O = P V (M128 N=D K128) written
-//                        over the first D columns of the same TMEM buffer
+//   mma      (2 threads) one issues S = Q K^T (M128 N128 K=D) tile after tile, the other
+//                        O = P V (M128 N=D K128), written over the first D columns of the
+//                        same TMEM buffer; each blocks on what its next tile needs, so a
+//                        tile that becomes ready is issued without a polling round
 //   softmax  (NB x 4 warps; warpgroup w owns tiles t = w mod NB)
 //            - gathers the 128 query rows of its *next* tile with 16-byte asynchronous
 //              copies, issued between the two passes over the current tile's scores: a
@@ -48,8 +50,8 @@ template <int D> struct FwdCfg {
   static constexpr int kPBytes = 2 * kSub;             // [128][128] 16-bit
   static constexpr int kSmemData = 2 * kOperand + kQStages * kOperand + kBufs * kPBytes;
   static constexpr int kSmem = kSmemData + 1024 /*align*/ + 10240 /*barriers, row tables*/;
-  static constexpr int kMmaWarp = 4 * kBufs, kLoadWarp = kMmaWarp + 1;
-  static constexpr int kThreads = (4 * kBufs + 2) * 32;
+  static constexpr int kMmaWarp = 4 * kBufs, kPvWarp = kMmaWarp + 1, kLoadWarp = kMmaWarp + 2;
+  static constexpr int kThreads = (4 * kBufs + 3) * 32;
 };
 
 struct Column {                            // one unit of work
@@ -63,7 +65,7 @@ struct Bars {
   uint64_t q_empty[4];                     // per stage: the S MMA that read it has retired
   uint64_t s_full[4], p_full[4], o_full[4], so_free[4];
   uint64_t col_full[4];                    // column descriptors published by the loader
-  uint64_t drain;                          // all MMAs of the CTA have completed
+  uint64_t drain[2];                       // all MMAs of an issuing thread have completed
   uint32_t tmem_base;
   int abort;
   Column cols[4];                          // ring: cols[i & 3] describes the CTA's i-th column; n < 0 ends the stream
@@ -91,13 +93,20 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return r;
 }
 
+// Work item `item` of the launch: the items of the (sequence, kv head) rows interleaved, each
+// row's in its dispatch order (heaviest first). To this kernel an item is a column of its
+// own: a block and a range of the block's pair list.
 __device__ __forceinline__ bool load_column(Column& c, int item, const moba_b200_index& ix,
                                             const moba_b200_problem& p, const int32_t* cu, int n_kv_rows) {
-  const int r = item / n_kv_rows;
   c.kv_row = item % n_kv_rows;
-  c.blk = ix.order[(size_t)c.kv_row * p.num_blocks + r];
-  c.n = ix.col_nnz[(size_t)c.kv_row * p.num_blocks + c.blk];
-  c.lo = ix.col_offsets[(size_t)c.kv_row * (p.num_blocks + 1) + c.blk];
+  WorkItem w;
+  if (!load_work_item(w, ix, ix.col_nnz + (size_t)c.kv_row * p.num_blocks, c.kv_row, item / n_kv_rows)) {
+    c.n = 0; c.keys = 0;
+    return false;
+  }
+  c.blk = w.blk;
+  c.n = w.n;
+  c.lo = ix.col_offsets[(size_t)c.kv_row * (p.num_blocks + 1) + c.blk] + w.first;
   const int seq = c.kv_row / p.kv_heads;
   const SeqSpan sp = seq_span(cu, p.packed, seq, p.tokens);
   c.b = p.packed ? 0 : (size_t)seq;
@@ -161,7 +170,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       mbar_init(&bars->o_full[i], 1); mbar_init(&bars->so_free[i], 128);
       mbar_init(&bars->col_full[i], 1);
     }
-    mbar_init(&bars->drain, 1);
+    mbar_init(&bars->drain[0], 1); mbar_init(&bars->drain[1], 1);
     bars->abort = 0;
     fence_barrier_init();
   }
@@ -220,6 +229,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
     // table, so one barrier per gather is enough (the table of gather g is rewritten by
     // gather g + 2, behind the barrier of gather g + 1).
     uint32_t n_gather = 0;
+    const uint64_t keep = l2_policy_evict_last();
     auto gather = [&](const Cur& k, int row, int head) {
       const bool live = (int)(k.t - k.t0) * kTile + r < k.c.n;
       int* tab = bars->q_row[wg][n_gather & 1];
@@ -234,8 +244,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       for (int pass = 0; pass < CPR; ++pass) {
         const int rr = pass * RPP + r / CPR;
         const int ri = tab[rr];
-        cp_async16(stage + (cc >> 3) * kSub + swz128(rr, cc & 7), q + (size_t)(ri < 0 ? 0 : ri) * D + cc * 8,
-                   ri < 0 ? 0u : 16u);
+        cp_async16_hint(stage + (cc >> 3) * kSub + swz128(rr, cc & 7), q + (size_t)(ri < 0 ? 0 : ri) * D + cc * 8,
+                        ri < 0 ? 0u : 16u, keep);
       }
       cp_async_commit();
     };
@@ -245,6 +255,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
     bool more = locate(pf, true) == 1;
     if (more) load_entry(pf, n_row, n_head, n_slot);
     bool gathered = false;
+    PHASE_CLOCK(ph);
     while (more) {
       const Cur cur = pf;
       const Column& c = cur.c;
@@ -257,6 +268,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         fence_proxy_async();
         mbar_arrive(&bars->q_full[wg]);
       }
+      PHASE_ADD(wc, 10, ph);                           // late gather
       int jmax = c.keys - 1;
       if (p.causal && live && (row - c.bos) / kTile == c.blk) jmax = min(jmax, row - c.key0);
       // Away from the diagonal block and the ragged ends every row keeps all 128 keys; such
@@ -270,6 +282,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       pf.t += NB;
       const int nxt = locate(pf, false);
       if (nxt == 1) load_entry(pf, n_row, n_head, n_slot);
+      PHASE_ADD(wc, 11, ph);                           // s_full wait, next tile located
 
       uint32_t v[32];
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -291,7 +304,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       }
       const float m2 = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * cs;
 
+      PHASE_ADD(wc, 12, ph);                           // first pass (row maximum)
       if (nxt == 1) gather(pf, n_row, n_head);
+      PHASE_ADD(wc, 13, ph);                           // copies of the next tile issued
 
       float l4[4] = {0.f, 0.f, 0.f, 0.f};
       auto exp_pass = [&](auto masked) {
@@ -319,11 +334,13 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       };
       if (all_open) exp_pass(std::false_type{}); else exp_pass(std::true_type{});
       const float l = (l4[0] + l4[1]) + (l4[2] + l4[3]);
+      PHASE_ADD(wc, 14, ph);                           // second pass (exp, P)
       if (nxt == 1) cp_async_wait<0>();                // the next tile's rows have landed
       fence_proxy_async();                             // P and those rows -> visible to the MMA
       tc_fence_before();
       mbar_arrive(&bars->p_full[wg]);
       if (nxt == 1) mbar_arrive(&bars->q_full[wg]);
+      PHASE_ADD(wc, 15, ph);                           // copies landed, fences, arrivals
 
       // ---- epilogue of the same tile: O sits in the first D columns of this buffer ----
       const float inv = 1.f / l;
@@ -332,6 +349,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       // A wait that gave up leaves TMEM unspecified: the tile then stores nothing.
       const bool o_ok = mbar_wait(&bars->o_full[wg], u & 1, wc, 3) && s_ok;
       tc_fence_after();
+      PHASE_ADD(wc, 16, ph);                           // o_full wait
 #pragma unroll 1
       for (int ch = 0; ch < D / 32; ++ch) {
         tmem_ld32(tbuf + ch * 32, v);
@@ -358,7 +376,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       }
       tc_fence_before();
       mbar_arrive(&bars->so_free[wg]);               // the TMEM buffer may be overwritten
-      if (live && o_ok) part_lse[dst_row] = m2 + log2f(l);
+      PHASE_ADD(wc, 17, ph);                           // O read and staged
+      if (live && o_ok) st_global_stream_f32(part_lse + dst_row, m2 + log2f(l));
       if (sizeof(TP) == 2) {
         bars->out_ptr[wg][r] = (live && o_ok) ? reinterpret_cast<unsigned char*>(dst) : nullptr;
         asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
@@ -370,10 +389,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
           const int rr = pass * RPPO + r / CPRO;
           unsigned char* op = bars->out_ptr[wg][rr];
           const uint4 w = *reinterpret_cast<const uint4*>(myP + (cc >> 3) * kSub + swz128(rr, cc & 7));
-          if (op != nullptr) *reinterpret_cast<uint4*>(op + cc * 16) = w;
+          if (op != nullptr) st_global_stream16(op + cc * 16, w);
         }
         asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");   // the staging area is P again
       }
+      PHASE_ADD(wc, 18, ph);                           // partial rows stored
 
       if (nxt == 1) { gathered = true; continue; }
       if (nxt == 0) break;
@@ -382,44 +402,34 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       gathered = false;
     }
   }
-  else if (warp == Cfg::kMmaWarp) {
-    // ============================== MMA issuer ==============================
-    // One thread feeds the tensor core. It polls instead of blocking so that whichever of
-    // "next S tile" and "next P.V tile" becomes possible first is issued first.
+  else if (warp == Cfg::kMmaWarp || warp == Cfg::kPvWarp) {
+    // ============================== MMA issuers ==============================
+    // Two threads feed the tensor core, each walking the CTA's tiles in order and blocking
+    // on exactly what its next MMA needs: a tile is issued as soon as its inputs are there.
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc(0, 128, 128, 0, 0);
       constexpr uint32_t idesc_o = make_idesc(0, 128, D, 0, 1);
       const uint32_t fbits = (fmt << 7) | (fmt << 10);
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), aP = smem_u32(sP);
-      struct Cursor { uint32_t it, pt; int i, nt, partial; bool have, end; };
-      Cursor cs_{0, 0, 0, 0, 0, false, false}, cp_{0, 0, 0, 0, 0, false, false};
-      auto refill = [&](Cursor& k) {
-        if (k.have || k.end) return;
-        if (!mbar_try_wait(&bars->col_full[k.it & 3], (k.it >> 2) & 1)) return;
-        const int n = bars->cols[k.it & 3].n;
-        if (n < 0) { k.end = true; return; }
-        k.nt = (n + kTile - 1) / kTile;
-        k.partial = bars->cols[k.it & 3].keys < kTile;
-        k.i = 0;
-        k.have = true;
-      };
-      auto step = [&](Cursor& k) {
-        if (++k.i == k.nt) { k.have = false; ++k.it; if (k.partial) ++k.pt; }
-      };
-      uint32_t ns = 0, np = 0, idle = 0;
-      while (true) {
-        bool progressed = false;
-        // ---- S = Q K^T of tile ns ----
-        refill(cs_);
-        if (cs_.have) {
-          const uint32_t b = ns % NB, u = ns / NB, qs = ns % NQ;
-          bool ok = mbar_try_wait(&bars->q_full[b], u & 1);
-          if (ok && u >= 1) ok = mbar_try_wait(&bars->so_free[b], (u - 1) & 1);
-          if (ok && cs_.i == 0) {
-            ok = mbar_try_wait(&bars->k_full, cs_.it & 1);
-            if (ok && cs_.partial) ok = mbar_try_wait(&bars->k_fix, cs_.pt & 1);
-          }
-          if (ok) {
+      const bool is_s = warp == Cfg::kMmaWarp;
+      uint32_t t = 0, pt = 0;                                   // tiles issued, cut-short columns seen
+      for (uint32_t it = 0;; ++it) {
+        if (!mbar_wait(&bars->col_full[it & 3], (it >> 2) & 1, wc, 20)) break;
+        const int n = bars->cols[it & 3].n;
+        if (n < 0) break;
+        const int nt = (n + kTile - 1) / kTile;
+        const bool partial = bars->cols[it & 3].keys < kTile;
+        for (int i = 0; i < nt; ++i, ++t) {
+          const uint32_t b = t % NB, u = t / NB;
+          if (is_s) {
+            // ---- S = Q K^T of tile t ----
+            const uint32_t qs = t % NQ;
+            mbar_wait(&bars->q_full[b], u & 1, wc, 21);
+            if (u >= 1) mbar_wait(&bars->so_free[b], (u - 1) & 1, wc, 22);
+            if (i == 0) {
+              mbar_wait(&bars->k_full, it & 1, wc, 23);
+              if (partial) mbar_wait(&bars->k_fix, pt & 1, wc, 23);
+            }
             tc_fence_after();
             const uint32_t qb = aQ + qs * Cfg::kOperand;
 #pragma unroll
@@ -430,53 +440,31 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
             }
             umma_commit(&bars->s_full[b]);
             umma_commit(&bars->q_empty[qs]);
-            if (cs_.i == cs_.nt - 1) umma_commit(&bars->k_free);
-            step(cs_);
-            ++ns;
-            progressed = true;
-          }
-        }
-        // ---- O = P V of tile np ----
-        if (np < ns) {
-          refill(cp_);
-          if (cp_.have) {
-            const uint32_t b = np % NB, u = np / NB;
-            bool ok = mbar_try_wait(&bars->p_full[b], u & 1);
-            if (ok && cp_.i == 0) {
-              ok = mbar_try_wait(&bars->v_full, cp_.it & 1);
-              if (ok && cp_.partial) ok = mbar_try_wait(&bars->v_fix, cp_.pt & 1);
+            if (i == nt - 1) umma_commit(&bars->k_free);
+          } else {
+            // ---- O = P V of tile t ----
+            mbar_wait(&bars->p_full[b], u & 1, wc, 24);
+            if (i == 0) {
+              mbar_wait(&bars->v_full, it & 1, wc, 25);
+              if (partial) mbar_wait(&bars->v_fix, pt & 1, wc, 25);
             }
-            if (ok) {
-              tc_fence_after();
-              const uint32_t pb = aP + b * Cfg::kPBytes;
+            tc_fence_after();
+            const uint32_t pb = aP + b * Cfg::kPBytes;
 #pragma unroll
-              for (int ks = 0; ks < 8; ++ks) {
-                umma_f16(tmem + b * 128, make_sdesc(pb + (ks >> 2) * kSub + (ks & 3) * 32, 16, 1024),
-                         make_sdesc(aV + ks * 2048, kSub, 1024), idesc_o | fbits, ks > 0);
-              }
-              umma_commit(&bars->o_full[b]);
-              if (cp_.i == cp_.nt - 1) umma_commit(&bars->v_free);
-              step(cp_);
-              ++np;
-              progressed = true;
+            for (int ks = 0; ks < 8; ++ks) {
+              umma_f16(tmem + b * 128, make_sdesc(pb + (ks >> 2) * kSub + (ks & 3) * 32, 16, 1024),
+                       make_sdesc(aV + ks * 2048, kSub, 1024), idesc_o | fbits, ks > 0);
             }
+            umma_commit(&bars->o_full[b]);
+            if (i == nt - 1) umma_commit(&bars->v_free);
           }
         }
-        if (cs_.end && np == ns) break;
-        if (progressed) { idle = 0; continue; }
-        if ((++idle & 1023u) == 0u) {
-          if (*wc.abort) break;
-          if (idle >= (1u << 24)) {                     // bounded: give up, flag the error
-            *wc.abort = 1;
-            atomicOr(error_word, kErrWaitTimeout);
-            break;
-          }
-        }
+        if (partial) ++pt;
       }
-      // Every MMA has completed before the CTA lets go of its TMEM, also on the way out of
-      // a run that gave up on a wait.
-      umma_commit(&bars->drain);
-      mbar_wait_quiet(&bars->drain, 0);
+      // Every MMA of this thread has completed before the CTA lets go of its TMEM, also on
+      // the way out of a run that gave up on a wait.
+      umma_commit(&bars->drain[is_s ? 0 : 1]);
+      mbar_wait_quiet(&bars->drain[is_s ? 0 : 1], 0);
     }
     __syncwarp();
   } else {
@@ -487,11 +475,28 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
     // zeroes the rows of a block that the end of its sequence cuts short (they belong to
     // the next sequence, or to the next batch row).
     uint32_t it_cnt = 0;
+    const uint64_t keep = l2_policy_evict_last();
     // The list is sorted longest first; CTAs take it in alternating direction
     // (0..G-1, G-1..0, ...) so that no CTA collects the largest of every round.
     const int G = (int)gridDim.x;
+    const size_t index_elems = (size_t)n_kv_rows * ix.capacity;
+    auto item_of = [&](int round) { return round * G + ((round & 1) ? (G - 1 - (int)blockIdx.x) : (int)blockIdx.x); };
+    // The index entries of a column are read by the softmax warps a tile at a time, straight
+    // from global memory; asking the L2 for them a column ahead turns a DRAM round trip per
+    // tile into an L2 hit.
+    auto prefetch_entries = [&](int round) {
+      const int item = item_of(round);
+      Column c;
+      if (round * G >= n_items || item >= n_items || !load_column(c, item, ix, p, cu, n_kv_rows)) return;
+      if (lane < 3) {
+        const int32_t* arr = lane == 0 ? ix.row_indices : (lane == 1 ? ix.head_indices : ix.slot_of_pair);
+        l2_prefetch_i32(arr, (size_t)c.kv_row * ix.capacity + c.lo, c.n, index_elems);
+      }
+    };
+    prefetch_entries(0);
     for (int round = 0; round * G < n_items; ++round) {
-      const int item = round * G + ((round & 1) ? (G - 1 - (int)blockIdx.x) : (int)blockIdx.x);
+      prefetch_entries(round + 1);
+      const int item = item_of(round);
       if (item >= n_items) continue;
       Column c;
       if (!load_column(c, item, ix, p, cu, n_kv_rows)) continue;
@@ -506,12 +511,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       if (it_cnt >= 1) mbar_wait(&bars->k_free, (it_cnt - 1) & 1, wc, 4);
       if (lane == 0) {
         mbar_expect_tx(&bars->k_full, Cfg::kOperand);
-        for (int s = 0; s < Cfg::kSubs; ++s) tma_load_3d(sK + s * kSub, &k_map, &bars->k_full, s * 64, kvh, tok0);
+        for (int s = 0; s < Cfg::kSubs; ++s) tma_load_3d_hint(sK + s * kSub, &k_map, &bars->k_full, s * 64, kvh, tok0, keep);
       }
       if (it_cnt >= 1) mbar_wait(&bars->v_free, (it_cnt - 1) & 1, wc, 5);
       if (lane == 0) {
         mbar_expect_tx(&bars->v_full, Cfg::kOperand);
-        for (int s = 0; s < Cfg::kSubs; ++s) tma_load_3d(sV + s * kSub, &v_map, &bars->v_full, s * 64, kvh, tok0);
+        for (int s = 0; s < Cfg::kSubs; ++s) tma_load_3d_hint(sV + s * kSub, &v_map, &bars->v_full, s * 64, kvh, tok0, keep);
       }
       if (c.keys < kTile) {
         const int dead = kTile - c.keys;
@@ -592,7 +597,13 @@ int launch_fwd_sm100(const moba_b200_problem& p, const void* q, const void* k, c
   if (rc) return rc;
   rc = encode_rows_map(&vm, v, rows, p.kv_heads, p.head_dim, 128);
   if (rc) return rc;
-  const int n_items = p.num_blocks * p.n_seq * p.kv_heads;
+  if (ix.work_items == nullptr || ix.items_per_row <= 0) {
+    set_error("forward: the index carries no work items (build it with moba_b200_transpose)");
+    return MOBA_B200_EINVAL;
+  }
+  const long long n_items_ll = (long long)ix.items_per_row * p.n_seq * p.kv_heads;
+  if (n_items_ll > 0x7fffffffLL) { set_error("forward: too many work items"); return MOBA_B200_EUNSUPPORTED; }
+  const int n_items = (int)n_items_ll;
   const bool bf = p.dtype == MOBA_B200_BF16;
 #define GO(D, T, TP) return launch_one<D, T, TP>(p, km, vm, q, ix, cu, part_o, part_lse, n_items, err, st)
   if (p.head_dim == 64) {

@@ -275,7 +275,7 @@ dq_reduce_kernel(const T* __restrict__ dq_part, const float* __restrict__ part_l
     for (int u = 0; u < kAhead; ++u) live[u] = (i0 + u < slots) && (ls[i0 + u] > -INFINITY);
 #pragma unroll
     for (int u = 0; u < kAhead; ++u)
-      raw[u] = live[u] ? *reinterpret_cast<const uint4*>(src + (size_t)(i0 + u) * d) : make_uint4(0, 0, 0, 0);
+      raw[u] = live[u] ? __ldcs(reinterpret_cast<const uint4*>(src + (size_t)(i0 + u) * d)) : make_uint4(0, 0, 0, 0);
 #pragma unroll
     for (int u = 0; u < kAhead; ++u) {
       if (!live[u]) continue;

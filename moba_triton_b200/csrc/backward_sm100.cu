@@ -6,7 +6,7 @@
 // Per tile of 128 gathered queries (five MMAs, all M = 128):
 //   S  = Q K^T            A Q  (K-major)   B K  (K-major)   N 128  -> TMEM [0,128)
 //   dP = dO V^T           A dO (K-major)   B V  (K-major)   N 128  -> TMEM [128,256)
-//   P  = exp2(S c - lse), dS = P (dP - delta)   (256 threads, 64 columns each) -> smem, 16-bit
+//   P  = exp2(S c - lse), dS = P (dP - delta)   (512 threads, 32 columns each) -> smem, 16-bit
 //   dV += P^T dO          A P  (M-major)   B dO (N-major)   N D    -> TMEM [256,256+D)
 //   dK += dS^T Q          A dS (M-major)   B Q  (N-major)   N D    -> TMEM [256+D,256+2D)
 //   dQ  = dS K            A dS (K-major)   B K  (N-major)   N D    -> TMEM [0,D)  (over S)
@@ -26,8 +26,10 @@ namespace {
 
 constexpr int kTile = 128;
 constexpr int kSub = kTile * 128;
-constexpr int kMmaWarp = 8, kLoadWarp = 9, kGatherWarp0 = 10;
-constexpr int kThreads = 14 * 32;
+constexpr int kElemWarps = 16;                           // four key quarters x four row groups
+constexpr int kElemThreads = 32 * kElemWarps;
+constexpr int kMmaWarp = kElemWarps, kLoadWarp = kMmaWarp + 1, kGatherWarp0 = kMmaWarp + 2;
+constexpr int kThreads = (kElemWarps + 6) * 32;
 
 template <int D> struct BwdCfg {
   static constexpr int kSubs = D / 64;
@@ -60,16 +62,25 @@ struct Bars {
 
 struct Column {
   int kv_row, blk, n, lo, key0, keys, bos;
+  int slot;      // dK/dV partial slot of this work item, -1: the item is the whole column
   size_t b;
 };
 
+// Work item `item` of the launch: the items of the (sequence, kv head) rows interleaved, each
+// row's in its dispatch order (heaviest first). An item is a block and a range of the block's
+// pair list; the items of a split column each own a dK/dV partial slot.
 __device__ __forceinline__ bool load_column(Column& c, int item, const moba_b200_index& ix,
                                             const moba_b200_problem& p, const int32_t* cu, int n_kv_rows) {
-  const int r = item / n_kv_rows;
   c.kv_row = item % n_kv_rows;
-  c.blk = ix.order[(size_t)c.kv_row * p.num_blocks + r];
-  c.n = ix.col_nnz[(size_t)c.kv_row * p.num_blocks + c.blk];
-  c.lo = ix.col_offsets[(size_t)c.kv_row * (p.num_blocks + 1) + c.blk];
+  WorkItem w;
+  if (!load_work_item(w, ix, ix.col_nnz + (size_t)c.kv_row * p.num_blocks, c.kv_row, item / n_kv_rows)) {
+    c.n = 0; c.keys = 0; c.slot = -1;                  // padding: nothing to do, nothing to zero
+    return false;
+  }
+  c.blk = w.blk;
+  c.n = w.n;
+  c.slot = w.slot;
+  c.lo = ix.col_offsets[(size_t)c.kv_row * (p.num_blocks + 1) + c.blk] + w.first;
   const int seq = c.kv_row / p.kv_heads;
   const SeqSpan sp = seq_span(cu, p.packed, seq, p.tokens);
   c.b = p.packed ? 0 : (size_t)seq;
@@ -121,8 +132,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                  const T* __restrict__ q, const T* __restrict__ dout, const float* __restrict__ lse,
                  const float* __restrict__ delta, moba_b200_index ix, const int32_t* __restrict__ cu,
-                 T* __restrict__ dq_part, T* __restrict__ dk, T* __restrict__ dv, moba_b200_problem p,
-                 int n_items, unsigned* error_word) {
+                 T* __restrict__ dq_part, float* __restrict__ dkv_scratch, T* __restrict__ dk, T* __restrict__ dv,
+                 moba_b200_problem p, int n_items, unsigned* error_word) {
   using Cfg = BwdCfg<D>;
   constexpr int NST = Cfg::kStages, NKV = Cfg::kKvBufs;
   extern __shared__ unsigned char smem_dyn[];
@@ -153,9 +164,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       mbar_init(&bars->qd_full[i], 128); mbar_init(&bars->qd_empty[i], 1);
     }
     mbar_init(&bars->k_fix, 128); mbar_init(&bars->v_fix, 128);
-    mbar_init(&bars->sp_full, 1); mbar_init(&bars->pds_full, 256);
-    mbar_init(&bars->dq_full, 1); mbar_init(&bars->dq_read, 256);
-    mbar_init(&bars->acc_full, 1); mbar_init(&bars->acc_read, 256); mbar_init(&bars->drain, 1);
+    mbar_init(&bars->sp_full, 1); mbar_init(&bars->pds_full, kElemThreads);
+    mbar_init(&bars->dq_full, 1); mbar_init(&bars->dq_read, kElemThreads);
+    mbar_init(&bars->acc_full, 1); mbar_init(&bars->acc_read, kElemThreads); mbar_init(&bars->drain, 1);
     bars->abort = 0;
     fence_barrier_init();
   }
@@ -172,12 +183,17 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
   const float cs = softmax_scale * kLog2e;
   const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
 
-  if (warp < 8) {
+  if (warp < kElemWarps) {
     // =========================== elementwise warps ===========================
-    const int wg = warp >> 2;                          // column half of the tile
+    // Sixteen warps: warp w works on TMEM lanes (tile rows) [32 (w mod 4), +32) and on key
+    // quarter w / 4 of the tile, i.e. 32 of a row's 128 scores. The tile's P / dS work is a
+    // fixed number of instructions; spread over sixteen warps, the loads from TMEM of one
+    // warp run under the arithmetic of the others.
+    const int wq = warp >> 2;                          // key quarter of the tile
     const int r = (warp & 3) * 32 + lane;              // tile row == TMEM lane
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     uint32_t t = 0, it_cnt = 0;
+    PHASE_CLOCK(ph);
     for (int round = 0; round * (int)gridDim.x < n_items; ++round) {
       const int item = snake_item(round);
       if (item >= n_items) continue;
@@ -185,8 +201,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       const bool work = load_column(c, item, ix, p, cu, n_kv_rows);
       const int kvh = c.kv_row % p.kv_heads;
       if (!work) {
-        if (c.keys > 0 && r < c.keys) {                // nobody selected this block: exact zeros
-          T* base = (wg == 0 ? dv : dk) + ((c.b * p.tokens + c.key0 + r) * p.kv_heads + kvh) * (size_t)D;
+        if (c.keys > 0 && r < c.keys && wq < 2) {      // nobody selected this block: exact zeros
+          T* base = (wq == 0 ? dv : dk) + ((c.b * p.tokens + c.key0 + r) * p.kv_heads + kvh) * (size_t)D;
           for (int i = 0; i < D / 8; ++i) reinterpret_cast<uint4*>(base)[i] = make_uint4(0, 0, 0, 0);
         }
         continue;
@@ -197,7 +213,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         // MMA warp waited for that before issuing S / dP, and sp_full follows those MMAs.
         // A wait that gave up leaves the stage's metadata stale or never written: the row then
         // counts as dead, so that no address is ever built from it.
+        PHASE_ADD(wc, 16, ph);                           // between tiles
         const bool sp_ok = mbar_wait(&bars->sp_full, t & 1, wc, 1);
+        PHASE_ADD(wc, 17, ph);                           // sp_full wait
         const int4 mt = sp_ok ? bars->meta[t % NST][r] : make_int4(-1, 0, 0, 0);
         const int row = mt.x < 0 ? 0 : mt.x, head = mt.y >> 8, slot = mt.y & 0xff;
         const bool live = mt.x >= 0;
@@ -207,103 +225,127 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         if (p.causal && live && (row - c.bos) / kTile == c.blk) jmax = min(jmax, row - c.key0);
 
         tc_fence_after();
-        uint32_t sv[32], pv[32];
         // Away from the diagonal block and the ragged ends every lane keeps all 128 keys;
         // such a tile runs without the per-element comparison.
         const bool all_open = __all_sync(0xffffffffu, jmax >= kTile - 1);
-        auto p_ds_half = [&](int hc, auto masked) {
-          const int col0 = wg * 64 + hc * 32;
-          tmem_ld32(tmem + lane_off + cS + col0, sv);
-          tmem_ld32(tmem + lane_off + cDP + col0, pv);
-          tmem_ld_wait();
-          unsigned char* p_sub = sP + wg * kSub;       // keys [64 wg, 64 wg + 64) live in sub-tile wg
-          unsigned char* s_sub = sS + wg * kSub;
+        PHASE_ADD(wc, 18, ph);                           // row metadata
+        {
+          unsigned char* p_sub = sP + (wq >> 1) * kSub;   // keys [64 h, 64 h + 64) live in sub-tile h
+          unsigned char* s_sub = sS + (wq >> 1) * kSub;
+          auto p_ds = [&](auto masked) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            float pe[8], ds[8];
+            for (int hc = 0; hc < 2; ++hc) {              // sixteen columns at a time: few live registers
+              uint32_t sv[16], pv[16];
+              const int col0 = wq * 32 + hc * 16;
+              tmem_ld16(tmem + lane_off + cS + col0, sv);
+              tmem_ld16(tmem + lane_off + cDP + col0, pv);
+              tmem_ld_wait();
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              const float x = ex2(fmaf(__uint_as_float(sv[g * 8 + k]), cs, -lse_r));
-              if constexpr (decltype(masked)::value) pe[k] = (col0 + g * 8 + k <= jmax) ? x : 0.f;
-              else pe[k] = x;
-              ds[k] = pe[k] * (__uint_as_float(pv[g * 8 + k]) - delta_r);
+              for (int g = 0; g < 2; ++g) {
+                float pe[8], ds[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                  const float x = ex2(fmaf(__uint_as_float(sv[g * 8 + k]), cs, -lse_r));
+                  if constexpr (decltype(masked)::value) pe[k] = (col0 + g * 8 + k <= jmax) ? x : 0.f;
+                  else pe[k] = x;
+                  ds[k] = pe[k] * (__uint_as_float(pv[g * 8 + k]) - delta_r);
+                }
+                uint4 wp, wd;
+                wp.x = pack2<T>(pe[0], pe[1]); wp.y = pack2<T>(pe[2], pe[3]);
+                wp.z = pack2<T>(pe[4], pe[5]); wp.w = pack2<T>(pe[6], pe[7]);
+                wd.x = pack2<T>(ds[0], ds[1]); wd.y = pack2<T>(ds[2], ds[3]);
+                wd.z = pack2<T>(ds[4], ds[5]); wd.w = pack2<T>(ds[6], ds[7]);
+                const uint32_t off = swz128(r, (wq & 1) * 4 + hc * 2 + g);
+                *reinterpret_cast<uint4*>(p_sub + off) = wp;
+                *reinterpret_cast<uint4*>(s_sub + off) = wd;
+              }
             }
-            uint4 wp, wd;
-            wp.x = pack2<T>(pe[0], pe[1]); wp.y = pack2<T>(pe[2], pe[3]);
-            wp.z = pack2<T>(pe[4], pe[5]); wp.w = pack2<T>(pe[6], pe[7]);
-            wd.x = pack2<T>(ds[0], ds[1]); wd.y = pack2<T>(ds[2], ds[3]);
-            wd.z = pack2<T>(ds[4], ds[5]); wd.w = pack2<T>(ds[6], ds[7]);
-            const uint32_t off = swz128(r, hc * 4 + g);
-            *reinterpret_cast<uint4*>(p_sub + off) = wp;
-            *reinterpret_cast<uint4*>(s_sub + off) = wd;
-          }
-        };
-        if (all_open) {
-#pragma unroll 1
-          for (int hc = 0; hc < 2; ++hc) p_ds_half(hc, std::false_type{});
-        } else {
-#pragma unroll 1
-          for (int hc = 0; hc < 2; ++hc) p_ds_half(hc, std::true_type{});
+          };
+          if (all_open) p_ds(std::false_type{}); else p_ds(std::true_type{});
         }
+        PHASE_ADD(wc, 19, ph);                           // P, dS: loads, arithmetic, stores
         fence_proxy_async();
         tc_fence_before();
         mbar_arrive(&bars->pds_full);
+        PHASE_ADD(wc, 20, ph);                           // fences, arrival
 
-        // ---- dQ rows of this tile: this warpgroup stores columns [wg D/2, (wg+1) D/2) ----
+        // ---- dQ rows of this tile: this quarter stores columns [wq D/4, (wq+1) D/4) ----
         const bool dq_ok = mbar_wait(&bars->dq_full, t & 1, wc, 2);
         tc_fence_after();
+        PHASE_ADD(wc, 21, ph);                           // dq_full wait
         // Stage the 16-bit dQ tile in shared memory (a tile of its own, or the P buffer once
         // dV has read it) so that eight or sixteen adjacent lanes write each row; one row per
         // thread straight to global memory would touch 32 lines per instruction.
-#pragma unroll 1
-        for (int ch = 0; ch < D / 64; ++ch) {
-          tmem_ld32(tmem + lane_off + cDQ + wg * (D / 2) + ch * 32, sv);
+        {
+          constexpr int QC = D / 4;                      // dQ columns of a quarter: 16 or 32
+          uint32_t qv[QC];
+          if constexpr (QC == 16) tmem_ld16(tmem + lane_off + cDQ + wq * QC, qv);
+          else tmem_ld32(tmem + lane_off + cDQ + wq * QC, qv);
           tmem_ld_wait();
-          const int c16 = wg * (D / 16) + ch * 4;          // first 16-byte chunk of these 32 columns
+          const int c16 = wq * (QC / 8);                 // first 16-byte chunk of these columns
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
+          for (int g = 0; g < QC / 8; ++g) {
             uint4 w;
-            w.x = pack2<T>(__uint_as_float(sv[g * 8 + 0]) * softmax_scale, __uint_as_float(sv[g * 8 + 1]) * softmax_scale);
-            w.y = pack2<T>(__uint_as_float(sv[g * 8 + 2]) * softmax_scale, __uint_as_float(sv[g * 8 + 3]) * softmax_scale);
-            w.z = pack2<T>(__uint_as_float(sv[g * 8 + 4]) * softmax_scale, __uint_as_float(sv[g * 8 + 5]) * softmax_scale);
-            w.w = pack2<T>(__uint_as_float(sv[g * 8 + 6]) * softmax_scale, __uint_as_float(sv[g * 8 + 7]) * softmax_scale);
+            w.x = pack2<T>(__uint_as_float(qv[g * 8 + 0]) * softmax_scale, __uint_as_float(qv[g * 8 + 1]) * softmax_scale);
+            w.y = pack2<T>(__uint_as_float(qv[g * 8 + 2]) * softmax_scale, __uint_as_float(qv[g * 8 + 3]) * softmax_scale);
+            w.z = pack2<T>(__uint_as_float(qv[g * 8 + 4]) * softmax_scale, __uint_as_float(qv[g * 8 + 5]) * softmax_scale);
+            w.w = pack2<T>(__uint_as_float(qv[g * 8 + 6]) * softmax_scale, __uint_as_float(qv[g * 8 + 7]) * softmax_scale);
             *reinterpret_cast<uint4*>(sO + ((c16 + g) >> 3) * kSub + swz128(r, (c16 + g) & 7)) = w;
           }
         }
         tc_fence_before();
         mbar_arrive(&bars->dq_read);                     // S / dQ columns may be overwritten
-        if (wg == 0) bars->out_ptr[r] = (live && dq_ok) ? reinterpret_cast<unsigned char*>(
+        if (wq == 0) bars->out_ptr[r] = (live && dq_ok) ? reinterpret_cast<unsigned char*>(
                                                    dq_part + ((qrow * p.slots) + slot) * (size_t)D) : nullptr;
-        asm volatile("bar.sync 2, 256;" ::: "memory");
+        PHASE_ADD(wc, 22, ph);                           // dQ read and staged
+        asm volatile("bar.sync 2, %0;" ::"n"(kElemThreads) : "memory");
         {
           constexpr int CPRO = D / 8;                    // 16-byte chunks per row
-          constexpr int RPPO = 256 / CPRO;               // rows per pass of the 256 threads
-          const int tid = wg * 128 + r;
+          constexpr int RPPO = kElemThreads / CPRO;      // rows per pass of the elementwise threads
+          const int tid = wq * 128 + r;
           const int cc = tid % CPRO;
 #pragma unroll
           for (int pass = 0; pass < kTile / RPPO; ++pass) {
             const int rr = pass * RPPO + tid / CPRO;
             unsigned char* op = bars->out_ptr[rr];
             const uint4 w = *reinterpret_cast<const uint4*>(sO + (cc >> 3) * kSub + swz128(rr, cc & 7));
-            if (op != nullptr) *reinterpret_cast<uint4*>(op + cc * 16) = w;
+            if (op != nullptr) st_global_stream16(op + cc * 16, w);
           }
         }
-        asm volatile("bar.sync 2, 256;" ::: "memory");   // the staging tile may be written again
+        asm volatile("bar.sync 2, %0;" ::"n"(kElemThreads) : "memory");   // the staging tile may be written again
+        PHASE_ADD(wc, 23, ph);                           // barriers and dQ stores
       }
-      // ---- the column's dV (warpgroup 0) and dK (warpgroup 1), one key row per thread ----
+      // ---- the column's dV (quarters 0, 1) and dK (quarters 2, 3): half of a key row per thread ----
       const bool acc_ok = mbar_wait(&bars->acc_full, it_cnt & 1, wc, 3);
       tc_fence_after();
       {
-        unsigned char* dst = reinterpret_cast<unsigned char*>(
-            (wg == 0 ? dv : dk) + ((c.b * p.tokens + c.key0 + r) * p.kv_heads + kvh) * (size_t)D);
-        const uint32_t col = (wg == 0) ? cDV : cDK;
-        const float sc = (wg == 0) ? 1.f : softmax_scale;
+        constexpr int HC = D / 2;                        // columns of a half
+        const uint32_t col = ((wq < 2) ? cDV : cDK) + (wq & 1) * HC;
+        const float sc = (wq < 2) ? 1.f : softmax_scale;
         uint32_t av[32];
+        if (c.slot < 0) {                                // the item is the whole column: final values
+          unsigned char* dst = reinterpret_cast<unsigned char*>(
+              (wq < 2 ? dv : dk) + ((c.b * p.tokens + c.key0 + r) * p.kv_heads + kvh) * (size_t)D + (wq & 1) * HC);
 #pragma unroll 1
-        for (int ch = 0; ch < D / 32; ++ch) {
-          tmem_ld32(tmem + lane_off + col + ch * 32, av);
-          tmem_ld_wait();
-          if (acc_ok && r < c.keys) store_row32<T>(dst + ch * 64, av, sc);
+          for (int ch = 0; ch < HC / 32; ++ch) {
+            tmem_ld32(tmem + lane_off + col + ch * 32, av);
+            tmem_ld_wait();
+            if (acc_ok && r < c.keys) store_row32<T>(dst + ch * 64, av, sc);
+          }
+        } else {                                         // one of several items of the column: float32 partial
+          float* dst = dkv_scratch + (((size_t)c.slot * 2 + (wq < 2 ? 0 : 1)) * kTile + r) * D + (wq & 1) * HC;
+#pragma unroll 1
+          for (int ch = 0; ch < HC / 32; ++ch) {
+            tmem_ld32(tmem + lane_off + col + ch * 32, av);
+            tmem_ld_wait();
+            if (acc_ok && r < c.keys) {
+#pragma unroll
+              for (int g = 0; g < 8; ++g)
+                reinterpret_cast<float4*>(dst + ch * 32)[g] =
+                    make_float4(__uint_as_float(av[g * 4 + 0]) * sc, __uint_as_float(av[g * 4 + 1]) * sc,
+                                __uint_as_float(av[g * 4 + 2]) * sc, __uint_as_float(av[g * 4 + 3]) * sc);
+            }
+          }
         }
       }
       tc_fence_before();
@@ -397,7 +439,22 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
     // ============================ K/V TMA loader ============================
     if (lane == 0) {
       uint32_t it_cnt = 0;
+      const uint64_t keep = l2_policy_evict_last();
+      const size_t index_elems = (size_t)n_kv_rows * ix.capacity;
+      // The gather warps read a column's index entries a tile at a time from global memory;
+      // asking the L2 for them a column ahead saves them a DRAM round trip per tile.
+      auto prefetch_entries = [&](int round) {
+        const int item = snake_item(round);
+        Column c;
+        if (round * (int)gridDim.x >= n_items || item >= n_items || !load_column(c, item, ix, p, cu, n_kv_rows)) return;
+        const size_t lo = (size_t)c.kv_row * ix.capacity + c.lo;
+        l2_prefetch_i32(ix.row_indices, lo, c.n, index_elems);
+        l2_prefetch_i32(ix.head_indices, lo, c.n, index_elems);
+        l2_prefetch_i32(ix.slot_of_pair, lo, c.n, index_elems);
+      };
+      prefetch_entries(0);
       for (int round = 0; round * (int)gridDim.x < n_items; ++round) {
+      prefetch_entries(round + 1);
       const int item = snake_item(round);
       if (item >= n_items) continue;
         Column c;
@@ -409,10 +466,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         if (ku >= 1) mbar_wait(&bars->kv_free[kb], (ku - 1) & 1, wc, 11);
         mbar_expect_tx(&bars->k_full[kb], Cfg::kOperand);
         for (int s = 0; s < Cfg::kSubs; ++s)
-          tma_load_3d(sK + kb * Cfg::kOperand + s * kSub, &k_map, &bars->k_full[kb], s * 64, kvh, tok0);
+          tma_load_3d_hint(sK + kb * Cfg::kOperand + s * kSub, &k_map, &bars->k_full[kb], s * 64, kvh, tok0, keep);
         mbar_expect_tx(&bars->v_full[kb], Cfg::kOperand);
         for (int s = 0; s < Cfg::kSubs; ++s)
-          tma_load_3d(sV + kb * Cfg::kOperand + s * kSub, &v_map, &bars->v_full[kb], s * 64, kvh, tok0);
+          tma_load_3d_hint(sV + kb * Cfg::kOperand + s * kSub, &v_map, &bars->v_full[kb], s * 64, kvh, tok0, keep);
         ++it_cnt;
       }
       // No load may be in flight into this CTA's shared memory when it exits.
@@ -427,6 +484,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
     // ========================= query / dO row gatherers =========================
     const int pt = threadIdx.x - kGatherWarp0 * 32;
     constexpr int CPR = D / 8, RPP = 128 / CPR;
+    const uint64_t keep = l2_policy_evict_last();
     uint32_t t = 0, it_cnt = 0;
     for (int round = 0; round * (int)gridDim.x < n_items; ++round) {
       const int item = snake_item(round);
@@ -481,8 +539,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
           const long long ro = bars->row_off[rr];
           const uint32_t o = (cc >> 3) * kSub + swz128(rr, cc & 7);
           const long long eo = (ro < 0 ? 0 : ro) + cc * 8;
-          cp_async16(stage_q + o, q + eo, ro < 0 ? 0u : 16u);
-          cp_async16(stage_g + o, dout + eo, ro < 0 ? 0u : 16u);
+          cp_async16_hint(stage_q + o, q + eo, ro < 0 ? 0u : 16u, keep);
+          cp_async16_hint(stage_g + o, dout + eo, ro < 0 ? 0u : 16u, keep);
         }
         cp_async_commit();
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -507,10 +565,46 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
 #endif
 }
 
+// dK / dV of the columns that were cut into several work items: one CTA per work item; the
+// CTA of a split column's first item adds the column's float32 partials in item order and
+// stores the result, every other CTA leaves at once.
+template <int D, typename T>
+__global__ void __launch_bounds__(256)
+dkv_reduce_kernel(const float* __restrict__ dkv_scratch, moba_b200_index ix, const int32_t* __restrict__ cu,
+                  T* __restrict__ dk, T* __restrict__ dv, moba_b200_problem p, int n_kv_rows) {
+  const int kv_row = blockIdx.x % n_kv_rows, j = blockIdx.x / n_kv_rows;
+  const int4 it = __ldg(reinterpret_cast<const int4*>(ix.work_items) + (size_t)kv_row * ix.items_per_row + j);
+  if (it.w < 0 || it.y != 0) return;                     // not the first item of a split column
+  const int nnz = ix.col_nnz[(size_t)kv_row * p.num_blocks + it.x];
+  const int tiles = (nnz + kTile - 1) / kTile;
+  const int n_chunks = (tiles + ix.chunk_tiles - 1) / ix.chunk_tiles;
+  const int seq = kv_row / p.kv_heads, kvh = kv_row % p.kv_heads;
+  const SeqSpan sp = seq_span(cu, p.packed, seq, p.tokens);
+  const size_t b = p.packed ? 0 : (size_t)seq;
+  const int key0 = sp.bos + it.x * kTile;
+  const int keys = min(kTile, sp.bos + sp.len - key0);
+  constexpr int V4 = D / 4;                              // float4 per row
+  for (int i = threadIdx.x; i < 2 * kTile * V4; i += 256) {
+    const int which = i / (kTile * V4), row = (i / V4) % kTile, c4 = i % V4;
+    if (row >= keys) continue;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c = 0; c < n_chunks; ++c) {
+      const float4 x = __ldcs(reinterpret_cast<const float4*>(
+          dkv_scratch + (((size_t)(it.w + c) * 2 + which) * kTile + row) * D) + c4);
+      acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+    }
+    T* dst = (which == 0 ? dv : dk) + ((b * p.tokens + key0 + row) * p.kv_heads + kvh) * (size_t)D + c4 * 4;
+    uint2 w;
+    w.x = pack2<T>(acc.x, acc.y);
+    w.y = pack2<T>(acc.z, acc.w);
+    *reinterpret_cast<uint2*>(dst) = w;
+  }
+}
+
 template <int D, typename T>
 int launch_one(const moba_b200_problem& p, const CUtensorMap& km, const CUtensorMap& vm, const void* q,
                const void* dout, const float* lse, const float* delta, const moba_b200_index& ix,
-               const int32_t* cu, void* dq_part, void* dk, void* dv, int n_items, unsigned* err,
+               const int32_t* cu, void* dq_part, float* dkv_scratch, void* dk, void* dv, int n_items, unsigned* err,
                cudaStream_t st) {
   auto kern = bwd_sm100_kernel<D, T>;
   MOBA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<D>::kSmem));
@@ -518,9 +612,15 @@ int launch_one(const moba_b200_problem& p, const CUtensorMap& km, const CUtensor
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = n_items < sms ? n_items : sms;
-  kern<<<grid, kThreads, BwdCfg<D>::kSmem, st>>>(km, vm, (const T*)q, (const T*)dout, lse, delta, ix, cu,
-                                                  (T*)dq_part, (T*)dk, (T*)dv, p, n_items, err);
-  MOBA_LAUNCH_OK("bwd_sm100_kernel");
+  {
+    KernelTimer timer__("bwd_sm100_kernel", st);
+    kern<<<grid, kThreads, BwdCfg<D>::kSmem, st>>>(km, vm, (const T*)q, (const T*)dout, lse, delta, ix, cu,
+                                                    (T*)dq_part, dkv_scratch, (T*)dk, (T*)dv, p, n_items, err);
+    MOBA_LAUNCH_OK("bwd_sm100_kernel");
+  }
+  KernelTimer timer__("dkv_reduce_kernel", st);
+  dkv_reduce_kernel<D, T><<<n_items, 256, 0, st>>>(dkv_scratch, ix, cu, (T*)dk, (T*)dv, p, p.n_seq * p.kv_heads);
+  MOBA_LAUNCH_OK("dkv_reduce_kernel");
   return MOBA_B200_OK;
 }
 
@@ -533,8 +633,7 @@ bool bwd_sm100_supported(const moba_b200_problem& p) {
 
 int launch_bwd_sm100(const moba_b200_problem& p, const void* q, const void* k, const void* v,
                      const void* dout, const float* lse, const float* delta, const moba_b200_index& ix,
-                     const int32_t* cu, void* dq_part, void* dk, void* dv, cudaStream_t st) {
-  KernelTimer timer__("bwd_sm100_kernel", st);
+                     const int32_t* cu, void* dq_part, float* dkv_scratch, void* dk, void* dv, cudaStream_t st) {
   unsigned* err = device_error_word();
   if (err == nullptr) { set_error("backward: no device error word"); return MOBA_B200_ECUDA; }
   CUtensorMap km, vm;
@@ -543,14 +642,21 @@ int launch_bwd_sm100(const moba_b200_problem& p, const void* q, const void* k, c
   if (rc) return rc;
   rc = encode_rows_map(&vm, v, rows, p.kv_heads, p.head_dim, 128);
   if (rc) return rc;
-  const int n_items = p.num_blocks * p.n_seq * p.kv_heads;
+  if (ix.work_items == nullptr || ix.items_per_row <= 0 || ix.chunk_tiles <= 0) {
+    set_error("backward: the index carries no work items (build it with moba_b200_transpose)");
+    return MOBA_B200_EINVAL;
+  }
+  if (dkv_scratch == nullptr) { set_error("backward: dkv_scratch is NULL"); return MOBA_B200_EINVAL; }
+  const long long n_items_ll = (long long)ix.items_per_row * p.n_seq * p.kv_heads;
+  if (n_items_ll > 0x7fffffffLL) { set_error("backward: too many work items"); return MOBA_B200_EUNSUPPORTED; }
+  const int n_items = (int)n_items_ll;
   const bool bf = p.dtype == MOBA_B200_BF16;
   if (p.head_dim == 64) {
-    if (bf) return launch_one<64, __nv_bfloat16>(p, km, vm, q, dout, lse, delta, ix, cu, dq_part, dk, dv, n_items, err, st);
-    return launch_one<64, __half>(p, km, vm, q, dout, lse, delta, ix, cu, dq_part, dk, dv, n_items, err, st);
+    if (bf) return launch_one<64, __nv_bfloat16>(p, km, vm, q, dout, lse, delta, ix, cu, dq_part, dkv_scratch, dk, dv, n_items, err, st);
+    return launch_one<64, __half>(p, km, vm, q, dout, lse, delta, ix, cu, dq_part, dkv_scratch, dk, dv, n_items, err, st);
   }
-  if (bf) return launch_one<128, __nv_bfloat16>(p, km, vm, q, dout, lse, delta, ix, cu, dq_part, dk, dv, n_items, err, st);
-  return launch_one<128, __half>(p, km, vm, q, dout, lse, delta, ix, cu, dq_part, dk, dv, n_items, err, st);
+  if (bf) return launch_one<128, __nv_bfloat16>(p, km, vm, q, dout, lse, delta, ix, cu, dq_part, dkv_scratch, dk, dv, n_items, err, st);
+  return launch_one<128, __half>(p, km, vm, q, dout, lse, delta, ix, cu, dq_part, dkv_scratch, dk, dv, n_items, err, st);
 }
 
 }  // namespace moba

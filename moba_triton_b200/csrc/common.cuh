@@ -90,6 +90,53 @@ __device__ __forceinline__ SeqSpan seq_span(const int32_t* cu, int packed, int s
   return s;
 }
 
+// ---- scheduling: columns are dispatched as work items of at most chunk_tiles tiles ----
+// Sizes are fixed functions of the problem record, so that the caller can allocate the
+// item table and the dK/dV partial slots without reading anything back from the device.
+constexpr int kSchedSMs = 148;               // the part this engine is written for
+constexpr int kSchedSplit = 4;               // a column above total / (kSchedSplit * SMs) tiles is cut
+constexpr int kMinChunkTiles = 8;
+
+static inline long long sched_pairs_bound(const moba_b200_problem& p) {
+  return (long long)p.batch * p.tokens * p.q_heads * p.slots;     // every (query head, slot) pair
+}
+static inline int sched_chunk_tiles(const moba_b200_problem& p) {
+  if (p.chunk_tiles > 0) return p.chunk_tiles;
+  const long long tiles = (sched_pairs_bound(p) + 127) / 128;
+  const long long t = (tiles + kSchedSplit * kSchedSMs - 1) / (kSchedSplit * kSchedSMs);
+  return t < kMinChunkTiles ? kMinChunkTiles : (int)(t > 0x3fffffff ? 0x3fffffff : t);
+}
+// Items beyond one per column: a column of n entries adds ceil(tiles / Tc) - 1 <= n / (128 Tc).
+static inline long long sched_extra_items(const moba_b200_problem& p) {
+  return sched_pairs_bound(p) / (128LL * sched_chunk_tiles(p)) + 1;
+}
+static inline long long sched_items_per_row(const moba_b200_problem& p) { return p.num_blocks + sched_extra_items(p); }
+// dK/dV partial slots: a split column of c items uses c slots, and c <= 2 (c - 1).
+static inline long long sched_part_slots(const moba_b200_problem& p) { return 2 * sched_extra_items(p) + 1; }
+static inline size_t sched_dkv_scratch_bytes(const moba_b200_problem& p) {
+  return (size_t)sched_part_slots(p) * 2 * 128 * p.head_dim * sizeof(float);
+}
+
+// One work item as the kernels see it.
+struct WorkItem {
+  int blk;        // block (column) of the (sequence, kv head) row
+  int first;      // first entry of the column's pair list this item covers
+  int n;          // entries it covers (0: an empty column)
+  int slot;       // dK/dV partial slot, -1: the item is the whole column
+};
+// Item `j` of row `kv_row`; false for padding. `col_nnz_row` is the row's col_nnz.
+__device__ __forceinline__ bool load_work_item(WorkItem& w, const moba_b200_index& ix, const int32_t* col_nnz_row,
+                                               int kv_row, int j) {
+  const int4 it = __ldg(reinterpret_cast<const int4*>(ix.work_items) + (size_t)kv_row * ix.items_per_row + j);
+  if (it.w == -2) return false;
+  w.blk = it.x;
+  w.first = it.y * 128;
+  const int nnz = col_nnz_row[it.x];
+  w.n = max(0, min(it.z * 128, nnz - w.first));
+  w.slot = it.w;
+  return true;
+}
+
 // ---- stage launchers (defined one per .cu file) -----------------------------
 int launch_pool(const moba_b200_problem& p, const void* k, const int32_t* cu, void* kbar,
                 cudaStream_t st);
@@ -102,12 +149,12 @@ bool gate_sm100_supported(const moba_b200_problem& p);
 size_t transpose_scratch_bytes(const moba_b200_problem& p);
 int launch_transpose(const moba_b200_problem& p, const int32_t* block_idx, const int32_t* cu,
                      int32_t* col_nnz, int32_t* col_offsets, int32_t* order, int32_t* rows,
-                     int32_t* heads, int32_t* slots, void* scratch, size_t scratch_bytes,
+                     int32_t* heads, int32_t* slots, int32_t* work_items, void* scratch, size_t scratch_bytes,
                      cudaStream_t st);
 
 int launch_transpose_noalloc(const moba_b200_problem& p, const int32_t* block_idx, const int32_t* cu,
                              int32_t* col_nnz, int32_t* col_offsets, int32_t* order, int32_t* rows,
-                             int32_t* heads, int32_t* slots, cudaStream_t st);
+                             int32_t* heads, int32_t* slots, int32_t* work_items, cudaStream_t st);
 
 int launch_fill_lse(const moba_b200_problem& p, float* part_lse, cudaStream_t st);
 int launch_fwd_portable(const moba_b200_problem& p, const void* q, const void* k, const void* v,
@@ -128,10 +175,18 @@ int launch_bwd_portable(const moba_b200_problem& p, const void* q, const void* k
                         void* dv, cudaStream_t st);
 int launch_bwd_sm100(const moba_b200_problem& p, const void* q, const void* k, const void* v,
                      const void* dout, const float* lse, const float* delta,
-                     const moba_b200_index& ix, const int32_t* cu, void* dq_part, void* dk,
-                     void* dv, cudaStream_t st);
+                     const moba_b200_index& ix, const int32_t* cu, void* dq_part, float* dkv_scratch,
+                     void* dk, void* dv, cudaStream_t st);
 bool bwd_sm100_supported(const moba_b200_problem& p);
 int launch_dq_reduce(const moba_b200_problem& p, const void* dq_part, const float* part_lse,
                      void* dq, cudaStream_t st);
+
+int launch_pack_index(const void* mask, int mask_bytes, int batch, int seq_len, int32_t* dest, int32_t* lengths,
+                      int32_t* cu, int32_t* meta, cudaStream_t st);
+int launch_seq_meta(const int32_t* cu, int n_seq, int32_t* meta, cudaStream_t st);
+int launch_pack_rows(const void* x, const int32_t* dest, const int32_t* cu, void* packed, int batch, int seq_len,
+                     size_t row_bytes, cudaStream_t st);
+int launch_unpack_rows(const void* packed, const int32_t* cu, void* out, int batch, int seq_len, size_t row_bytes,
+                       cudaStream_t st);
 
 }  // namespace moba

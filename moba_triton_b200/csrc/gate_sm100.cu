@@ -6,17 +6,23 @@
 // blocks a tile is exactly one block, so every row of a tile has the same
 // candidates: the blocks before the tile's own. Roles:
 //   loader (1 thread)  TMA: the unit's Q tile, then block-mean chunks of 128 blocks
-//   mma    (1 thread)  S = Q Kbar^T (M128 N128 K=D) into one of two TMEM buffers
-//   select (2 x 4 warps, alternating chunks) tcgen05.ld, one row per thread.
-//          A score can enter a row's list only if it exceeds the score of the
-//          list's last entry (candidates arrive in ascending block order, so an
-//          equal score never wins). That test is one float compare per score;
-//          the few that pass are appended, by predicated stores, to a small
-//          per-thread buffer in shared memory, and the buffer is emptied into the
-//          row's sorted register list of L keys whenever some lane of the warp is
-//          about to run out of room. A key is the score rounded to the input dtype
-//          and made monotone in the high half and 0xFFFF - block id in the low half,
-//          so "score descending, ties to the lower id" is plain integer order.
+//   mma    (1 thread)  S = Q Kbar^T (M128 N128 K=D) into one of two TMEM buffers, every
+//                      chunk of the unit once, then every chunk again
+//   select (2 x 4 warps; warpgroup w takes columns [64 w, 64 w + 64) of every chunk)
+//          tcgen05.ld, one row per thread. The chunks of a unit are scored twice.
+//          The first pass only keeps, per row, the maxima of eight interleaved subsets
+//          of the scores (one max per score): the L-th largest of them is a score that
+//          at least L candidates reach, so nothing below it can be selected. The second
+//          pass tests every score against that bound with one compare and appends the
+//          few that pass, by predicated stores, to a small per-thread buffer in shared
+//          memory; the buffer is emptied into the row's sorted register list of L keys
+//          whenever some lane of the warp is about to run out of room, which also
+//          raises the bound to the score of the list's last entry (candidates arrive
+//          in ascending block order, so an equal score never wins). A key is the score
+//          rounded to the input dtype and made monotone in the high half and
+//          0xFFFF - block id in the low half, so "score descending, ties to the lower
+//          id" is plain integer order. Scoring twice costs tensor-core time the gate has
+//          to spare; ranking every score once would cost issue slots it has not.
 // At the end of a unit the two warpgroups' lists are merged and each thread emits
 // its ids plus the own block, ascending, -1 padded.
 //
@@ -102,6 +108,17 @@ __device__ __forceinline__ float entry_bar(uint32_t key) {
   return widen16<T>(b);
 }
 
+// The largest score that is certainly below every score whose rounding to T is at least
+// round_T(m): one step of T under round_T(m), widened back to float.
+template <typename T>
+__device__ __forceinline__ float one_step_below(float m) {
+  if (!(m > -INFINITY)) return -INFINITY;
+  const uint32_t key = make_key<T>(m, 0u);
+  const uint32_t mono = key >> 16;
+  if (mono == 0u) return -INFINITY;
+  return entry_bar<T>(((mono - 1u) << 16) | 1u);
+}
+
 // Which unit a CTA takes in its `round`-th turn: heaviest units first, alternating
 // direction, so that no CTA collects the heaviest unit of every round.
 __device__ __forceinline__ int unit_of(int round) {
@@ -143,7 +160,10 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
   const int group = p.q_heads / p.kv_heads;
   const int take = p.take;
 #ifdef MOBA_WAIT_STATS
-  const WaitCtx wc{&bars->abort, error_word, nullptr};
+  __shared__ unsigned long long wait_stats[32];
+  if (threadIdx.x < 32) wait_stats[threadIdx.x] = 0;
+  const long long kernel_t0 = clock64();
+  const WaitCtx wc{&bars->abort, error_word, wait_stats};
 #else
   const WaitCtx wc{&bars->abort, error_word};
 #endif
@@ -152,7 +172,7 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     mbar_init(&bars->q_full, 1); mbar_init(&bars->q_free, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->kb_full[i], 1); mbar_init(&bars->kb_empty[i], 1);
-      mbar_init(&bars->s_full[i], 1); mbar_init(&bars->s_free[i], 128);
+      mbar_init(&bars->s_full[i], 1); mbar_init(&bars->s_free[i], 256);
     }
     mbar_init(&bars->drain, 1);
     bars->abort = 0;
@@ -165,9 +185,9 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
 
-  // Every role walks the same units and counts the same chunks: `gc` is the number of
-  // chunks of all earlier units of this CTA, and chunk c of a unit uses Kbar stage and
-  // TMEM buffer (gc + c) & 1.
+  // Every role walks the same units and counts the same steps: a unit of n chunks takes 2 n
+  // steps (chunk `step mod n`), `gc` is the number of steps of all earlier units of this CTA,
+  // and a step uses Kbar stage and TMEM buffer (gc + step) & 1.
   if (warp < 8) {
     // ================================ select ================================
     const int wg = warp >> 2;
@@ -181,7 +201,8 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     // warpgroup 0 only ever reads and overwrites words of its own.
     const uint32_t xk0 = smem_u32(sBuf) + (uint32_t)r * 8u;
     static_assert((L + 1) / 2 <= CAP, "a list fits the slots of one thread");
-    uint32_t gc = 0, used = 0;                                  // used: chunks this warpgroup has taken so far
+    uint32_t gc = 0;
+    PHASE_CLOCK(ph);
     for (int round = 0; round * (int)gridDim.x < n_units; ++round) {
       const int ui = unit_of(round);
       if (ui >= n_units) continue;
@@ -190,9 +211,13 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
       uint32_t best[L];
 #pragma unroll
       for (int e = 0; e < L; ++e) best[e] = 0u;                 // 0 sorts below every real key
+      float mx[8];                                              // first pass: maxima of 8 column subsets
+#pragma unroll
+      for (int e = 0; e < 8; ++e) mx[e] = -INFINITY;
       float bar = -INFINITY;                                    // a score must exceed this to be appended
       uint32_t wa = buf0;                                       // address of the next free slot
       auto flush = [&]() {                                      // whole warp: empty the buffers into the lists
+        PHASE_CLOCK(fl);
         while (__any_sync(0xffffffffu, wa != buf0)) {
           uint32_t key = 0u;
           if (wa != buf0) {
@@ -203,43 +228,70 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
           }
           list_offer<L>(best, key);
         }
-        bar = entry_bar<T>(best[L - 1]);
+        bar = fmaxf(bar, entry_bar<T>(best[L - 1]));
+        PHASE_ADD(wc, 4, fl);                                   // flushes (also counted in their phase)
       };
-      // the two warpgroups take alternate chunks of the same 128 rows
-      for (int c = (int)((wg - gc) & 1u); c < u.n_chunks; c += 2, ++used) {
-        const bool s_ok = mbar_wait(&bars->s_full[wg], used & 1, wc);
+      PHASE_ADD(wc, 1, ph);                                     // unit set-up
+      for (int step = 0; step < 2 * u.n_chunks; ++step) {
+        const uint32_t gidx = gc + (uint32_t)step, st = gidx & 1u;
+        const bool second = step >= u.n_chunks;
+        const int c = second ? step - u.n_chunks : step;
+        if (second && c == 0) {
+          // The L-th largest of the eight subset maxima: at least L candidates reach it.
+          float lo1 = INFINITY, lo2 = INFINITY;                 // smallest and second smallest
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            lo2 = fminf(lo2, fmaxf(lo1, mx[e]));
+            lo1 = fminf(lo1, mx[e]);
+          }
+          bar = one_step_below<T>(L >= 8 ? lo1 : lo2);
+        }
+        const bool s_ok = mbar_wait(&bars->s_full[st], (gidx >> 1) & 1u, wc, 9);
         tc_fence_after();
-        const int c0 = c * kTile;
-        const int cmax = u.tile - c0;                           // columns [0, cmax) are candidates
-        const bool full = cmax >= kTile;
+        PHASE_ADD(wc, 2, ph);                                   // s_full wait
+        const int c0 = c * kTile + wg * 64;                     // first column of this warpgroup's half
+        const int cmax = u.tile - c0;                           // its columns [0, cmax) are candidates
         const bool run = __all_sync(0xffffffffu, s_ok);         // a wait gave up: rank nothing unseen
         uint32_t v[32];
 #pragma unroll 1
-        for (int ch = 0; ch < 4; ++ch) {
-          tmem_ld32(tmem + lane_off + wg * 128 + ch * 32, v);
+        for (int h = 0; h < 2; ++h) {
+          tmem_ld32(tmem + lane_off + st * 128 + wg * 64 + h * 32, v);
           tmem_ld_wait();
-          if (ch == 3) { tc_fence_before(); mbar_arrive(&bars->s_free[wg]); }   // the scores are in registers
-          if (!run || ch * 32 >= cmax) continue;
-          if (!full) {
+          if (h == 1) { tc_fence_before(); mbar_arrive(&bars->s_free[st]); }   // the scores are in registers
+          if (!run || h * 32 >= cmax) continue;
+          if (cmax < h * 32 + 32) {
 #pragma unroll
             for (int k = 0; k < 32; ++k)
-              if (ch * 32 + k >= cmax) v[k] = 0xff800000u;      // -inf: never passes
+              if (h * 32 + k >= cmax) v[k] = 0xff800000u;       // -inf: never a candidate
           }
+          if (!second) {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) mx[k & 7] = fmaxf(mx[k & 7], __uint_as_float(v[k]));
+            continue;
+          }
+          const uint32_t col0 = (uint32_t)(c0 + h * 32);
 #pragma unroll
           for (int k0 = 0; k0 < 32; k0 += STEP) {
             if (__any_sync(0xffffffffu, wa > buf0 + (CAP - STEP) * kSlot)) flush();   // room for STEP more
 #pragma unroll
             for (int k = k0; k < k0 + STEP; ++k) {
-              if (__uint_as_float(v[k]) > bar) {
-                asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(wa), "r"(v[k]), "r"((uint32_t)(c0 + ch * 32 + k)) : "memory");
-                wa += kSlot;
-              }
+              // if (score > bar) { slot <- (score, block id); next slot }, predicated: a branch
+              // here would be taken by some lane of the warp at almost every score
+              asm volatile(
+                  "{\n\t.reg .pred p;\n\t"
+                  "setp.gt.f32 p, %1, %2;\n\t"
+                  "@p st.shared.v2.b32 [%0], {%3, %4};\n\t"
+                  "@p add.u32 %0, %0, %5;\n\t}"
+                  : "+r"(wa)
+                  : "f"(__uint_as_float(v[k])), "f"(bar), "r"(v[k]), "r"(col0 + (uint32_t)k), "n"(kTile * 8)
+                  : "memory");
             }
           }
         }
+        PHASE_ADD(wc, 3, ph);                                   // loads, maxima / tests and appends, flushes
       }
       flush();
-      gc += (uint32_t)u.n_chunks;
+      gc += 2u * (uint32_t)u.n_chunks;
       // ---- merge the two warpgroups' lists (warpgroup 1 -> warpgroup 0's empty buffer) ----
       asm volatile("bar.sync 2, 256;" ::: "memory");            // warpgroup 0 has emptied its buffer
       if (wg == 1) {
@@ -279,20 +331,21 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
       }
       // Warpgroup 0 reads the exchange area (its own buffer) before it appends to it again;
       // warpgroup 1 writes there only behind the first barrier of the next unit.
+      PHASE_ADD(wc, 5, ph);                                     // last flush, merge, emit
     }
   } else if (warp == kMmaWarp) {
     if (lane == 0) {
       const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
       const uint32_t idesc = make_idesc(0, 128, 128, 0, 0) | (fmt << 7) | (fmt << 10);
       const uint32_t aQ = smem_u32(sQ);
-      uint32_t gc = 0, nq = 0;                                  // chunks / Q tiles consumed so far
+      uint32_t gc = 0, nq = 0;                                  // steps / Q tiles consumed so far
       for (int round = 0; round * (int)gridDim.x < n_units; ++round) {
         const int ui = unit_of(round);
         if (ui >= n_units) continue;
         Unit u;
         if (!load_unit(u, ui, p, cu, n_tiles) || u.n_chunks == 0) continue;
         mbar_wait(&bars->q_full, nq & 1, wc);
-        for (int c = 0; c < u.n_chunks; ++c, ++gc) {
+        for (int step = 0; step < 2 * u.n_chunks; ++step, ++gc) {
           const uint32_t st = gc & 1, use = gc >> 1;
           const uint32_t aK = smem_u32(sKb) + st * Cfg::kOperand;
           mbar_wait(&bars->kb_full[st], use & 1, wc);
@@ -331,8 +384,9 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         mbar_expect_tx(&bars->q_full, Cfg::kOperand);
         for (int s = 0; s < Cfg::kSubs; ++s) tma_load_3d(sQ + s * kSub, &q_map, &bars->q_full, s * 64, u.hq, tok0);
         ++nq;
-        for (int c = 0; c < u.n_chunks; ++c, ++gc) {
+        for (int step = 0; step < 2 * u.n_chunks; ++step, ++gc) {
           const uint32_t st = gc & 1, use = gc >> 1;
+          const int c = step >= u.n_chunks ? step - u.n_chunks : step;
           if (use >= 1) mbar_wait(&bars->kb_empty[st], (use - 1) & 1, wc);
           if (*wc.abort) break;
           mbar_expect_tx(&bars->kb_full[st], Cfg::kOperand);
@@ -354,6 +408,12 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
   tc_fence_before();
   __syncthreads();
   if (warp == kMmaWarp) tmem_dealloc(tmem, 256);
+#ifdef MOBA_WAIT_STATS
+  if (threadIdx.x < 32 && blockIdx.x < 148) {
+    unsigned long long* out = reinterpret_cast<unsigned long long*>(error_word + 64) + (size_t)blockIdx.x * 32;
+    out[threadIdx.x] = threadIdx.x == 31 ? (unsigned long long)(clock64() - kernel_t0) : wait_stats[threadIdx.x];
+  }
+#endif
 }
 
 

@@ -58,6 +58,22 @@ struct WaitCtx {
 #endif
 };
 
+// Debug builds (MOBA_WAIT_STATS) also time the phases of a role: PHASE_CLOCK(t) starts a
+// clock, PHASE_ADD(ctx, site, t) adds the clocks since to counter `site` (lane 0 of each warp)
+// and restarts it. Both vanish from normal builds.
+#ifdef MOBA_WAIT_STATS
+#define PHASE_CLOCK(t) long long t = clock64()
+#define PHASE_ADD(ctx, site, t)                                                              \
+  do {                                                                                        \
+    const long long now__ = clock64();                                                        \
+    if ((ctx).stats != nullptr && (threadIdx.x & 31) == 0) atomicAdd(&(ctx).stats[site], (unsigned long long)(now__ - t)); \
+    t = now__;                                                                                \
+  } while (0)
+#else
+#define PHASE_CLOCK(t) do {} while (0)
+#define PHASE_ADD(ctx, site, t) do {} while (0)
+#endif
+
 constexpr long long kWaitCycles = 1ll << 31;   // about a second of SM clock
 constexpr uint32_t kSuspendNs = 4000;          // a try may sleep this long; completion wakes it at once
 
@@ -125,6 +141,39 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// L2 eviction policies. Rows that are gathered again and again (Q, dO, K, V) are loaded
+// "evict last"; the partial buffers, which are written once and read once by a later
+// kernel, are stored "evict first", so that their stream does not push the reused rows
+// out of the L2.
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ void cp_async16_hint(uint32_t dst_smem, const void* src, uint32_t src_bytes, uint64_t pol) {
+  asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;" ::"r"(dst_smem), "l"(src), "r"(src_bytes), "l"(pol)
+               : "memory");
+}
+__device__ __forceinline__ void st_global_stream16(void* dst, const uint4& w) {
+  asm volatile("st.global.cs.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(w.x), "r"(w.y), "r"(w.z), "r"(w.w) : "memory");
+}
+__device__ __forceinline__ void st_global_stream_f32(float* dst, float v) {
+  asm volatile("st.global.cs.f32 [%0], %1;" ::"l"(dst), "f"(v) : "memory");
+}
+
+// Asks the L2 to fetch [p, p + bytes) (both multiples of 16); nothing waits for it.
+__device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+// Prefetches elements [lo, lo + n) of an int32 array of `total` elements.
+__device__ __forceinline__ void l2_prefetch_i32(const int32_t* base, size_t lo, int n, size_t total) {
+  const size_t b0 = (lo * 4) & ~size_t(15);
+  size_t b1 = ((lo + (size_t)n) * 4 + 15) & ~size_t(15);
+  const size_t end = (total * 4) & ~size_t(15);
+  if (b1 > end) b1 = end;
+  if (b1 > b0) l2_prefetch_bulk(reinterpret_cast<const unsigned char*>(base) + b0, (uint32_t)(b1 - b0));
+}
+
 // A global load the compiler may not move: used to fetch index entries a tile or two before
 // they are needed (a plain load may be sunk to its first use, which defeats the prefetch).
 __device__ __forceinline__ int ld_nc_pinned(const int32_t* p) {
@@ -144,6 +193,13 @@ __device__ __forceinline__ float ld_nc_pinned_f(const float* p) {
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_hint(void* dst_smem, const CUtensorMap* m, uint64_t* bar, int c0,
+                                                 int c1, int c2, uint64_t pol) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;"
+      ::"r"(smem_u32(dst_smem)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "l"(pol)
+      : "memory");
 }
 __device__ __forceinline__ void tma_load_3d(void* dst_smem, const CUtensorMap* m, uint64_t* bar, int c0,
                                             int c1, int c2) {
@@ -213,6 +269,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
         "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
         "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+// 32 lanes x 16 consecutive float32 columns
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
 }

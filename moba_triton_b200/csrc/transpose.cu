@@ -9,7 +9,10 @@
 //   3. offsets  per (sequence, kv head): exclusive scan over blocks ->
 //               col_offsets, and the longest-first dispatch order (stable
 //               descending sort of col_nnz, by rank counting)
-//   4. scatter  one CTA per (row chunk, sequence, query head): its warps split the
+//   4. items    per (sequence, kv head): walks the columns in dispatch order and cuts
+//               each into work items of at most chunk_tiles tiles; a split column's
+//               items get consecutive dK/dV partial slots
+//   5. scatter  one CTA per (row chunk, sequence, query head): its warps split the
 //               chunk's rows into consecutive runs; a per-warp histogram and a scan
 //               over the warps give each warp its own cursors, and every warp then
 //               walks its run in order, ranks equal blocks inside the warp with
@@ -20,6 +23,7 @@
 // which claim positions with an atomic cursor and therefore leave the order
 // inside a column to the scheduler.
 #include "common.cuh"
+#include "sm100.cuh"
 
 #include <mutex>
 
@@ -34,11 +38,13 @@ static inline TransposeGeom transpose_geom(const moba_b200_problem& p) {
   while ((p.max_seqlen + r - 1) / r > 256) r <<= 1;
   return TransposeGeom{r, (p.max_seqlen + r - 1) / r};
 }
-size_t transpose_scratch_bytes(const moba_b200_problem& p) {
+static inline size_t tile_count_bytes(const moba_b200_problem& p) {
   const TransposeGeom g = transpose_geom(p);
   const size_t group = p.q_heads / p.kv_heads;
   return (size_t)p.n_seq * p.kv_heads * p.num_blocks * group * g.chunks * sizeof(int32_t);
 }
+// the per-chunk histograms, then one 16-byte cell holding the counter of dK/dV partial slots
+size_t transpose_scratch_bytes(const moba_b200_problem& p) { return ((tile_count_bytes(p) + 15) & ~size_t(15)) + 16; }
 
 __device__ __forceinline__ size_t block_idx_row(const moba_b200_problem& p, int seq, int hq,
                                                 int bos, int row) {
@@ -48,8 +54,9 @@ __device__ __forceinline__ size_t block_idx_row(const moba_b200_problem& p, int 
 
 __global__ void __launch_bounds__(256)
 count_kernel(const int32_t* __restrict__ block_idx, const int32_t* __restrict__ cu,
-             int32_t* __restrict__ tile_counts, moba_b200_problem p, int R, int C) {
+             int32_t* __restrict__ tile_counts, int32_t* __restrict__ slot_counter, moba_b200_problem p, int R, int C) {
   extern __shared__ int hist[];
+  if (blockIdx.x == 0 && threadIdx.x == 0) *slot_counter = 0;     // claimed from by work_items_kernel, two launches on
   const int chunk = blockIdx.x % C, y = blockIdx.x / C;
   const int seq = y / p.q_heads, hq = y % p.q_heads;
   const SeqSpan sp = seq_span(cu, p.packed, seq, p.tokens);
@@ -176,6 +183,88 @@ offsets_order_kernel(const int32_t* __restrict__ col_nnz, int32_t* __restrict__ 
   if (i < nb && part == 0) ord[rank] = i;
 }
 
+// One CTA per (sequence, kv head) row: the row's work items. Columns are taken in dispatch
+// order (longest first); a column of more than `tc` tiles becomes ceil(tiles / tc) items,
+// each with a dK/dV partial slot of its own. The slots of a row are consecutive and claimed
+// from a counter, so rows may claim in any order: slot numbers name scratch memory, results
+// do not depend on them.
+__global__ void __launch_bounds__(1024)
+work_items_kernel(const int32_t* __restrict__ col_nnz, const int32_t* __restrict__ order, int4* __restrict__ items,
+                  int32_t* __restrict__ slot_counter, int nb, int items_per_row, int tc, int slot_cap,
+                  unsigned* error_word) {
+  __shared__ long long warp_sums[32];
+  __shared__ long long carry_s;
+  __shared__ int base_s;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int32_t* nnz = col_nnz + (size_t)blockIdx.x * nb;
+  const int32_t* ord = order + (size_t)blockIdx.x * nb;
+  int4* out = items + (size_t)blockIdx.x * items_per_row;
+  auto chunks_of = [&](int r, int& blk, int& tiles) {
+    blk = ord[r];
+    tiles = (nnz[blk] + 127) / 128;
+    return tiles <= tc ? 1 : (tiles + tc - 1) / tc;
+  };
+  // (items, partial slots) of the row, summed as one 64-bit pair
+  auto block_scan = [&](long long v, long long& total) {
+    long long incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const long long t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    __syncthreads();
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    long long before = 0, all = 0;
+    for (int w = 0; w < 32; ++w) {
+      const long long s = warp_sums[w];
+      before += (w < warp) ? s : 0;
+      all += s;
+    }
+    total = all;
+    return before + incl - v;
+  };
+  // pass 1: how many partial slots the row needs
+  long long mine = 0;
+  for (int r = threadIdx.x; r < nb; r += 1024) {
+    int blk, tiles;
+    const int c = chunks_of(r, blk, tiles);
+    mine += (c > 1) ? c : 0;
+  }
+  long long row_slots;
+  block_scan(mine, row_slots);
+  if (threadIdx.x == 0) {
+    base_s = row_slots > 0 ? atomicAdd(slot_counter, (int)row_slots) : 0;
+    carry_s = 0;
+    if (row_slots > 0 && base_s + row_slots > slot_cap) atomicOr(error_word, 2u);   // sizes were promised by the host
+  }
+  __syncthreads();
+  const int base = base_s;
+  // pass 2: place the items
+  for (int r0 = 0; r0 < nb; r0 += 1024) {
+    const int r = r0 + threadIdx.x;
+    int blk = 0, tiles = 0, c = 0;
+    if (r < nb) c = chunks_of(r, blk, tiles);
+    const long long v = (long long)c | ((long long)(c > 1 ? c : 0) << 32);
+    long long total;
+    const long long carry = carry_s;
+    const long long at = carry + block_scan(v, total);
+    const int item0 = (int)(at & 0xffffffffLL), slot0 = (int)(at >> 32);
+    for (int i = 0; i < c; ++i) {
+      if (item0 + i >= items_per_row) { atomicOr(error_word, 2u); break; }
+      // beyond the promised capacity (flagged above) an item falls back to "whole column":
+      // wrong sums, reported through the error word, but no access outside the scratch
+      const int slot = (c > 1 && base + slot0 + i < slot_cap) ? base + slot0 + i : -1;
+      out[item0 + i] = make_int4(blk, i * tc, tiles == 0 ? 0 : min(tc, tiles - i * tc), slot);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) carry_s = carry + total;
+    __syncthreads();
+  }
+  const int used = (int)(carry_s & 0xffffffffLL);
+  for (int j = used + threadIdx.x; j < items_per_row; j += 1024) out[j] = make_int4(0, 0, 0, -2);   // padding
+}
+
 // One CTA of W warps per (row chunk, sequence, query head). The walk of a run is one
 // dependent chain per warp (match, cursor, store), so the chunk is cut into W runs that are
 // walked side by side: a histogram per run and a scan over the runs (both in shared memory)
@@ -290,7 +379,7 @@ static int launch_scatter(const moba_b200_problem& p, const int32_t* block_idx, 
 
 int launch_transpose(const moba_b200_problem& p, const int32_t* block_idx, const int32_t* cu,
                      int32_t* col_nnz, int32_t* col_offsets, int32_t* order, int32_t* rows,
-                     int32_t* heads, int32_t* slots, void* scratch, size_t scratch_bytes,
+                     int32_t* heads, int32_t* slots, int32_t* work_items, void* scratch, size_t scratch_bytes,
                      cudaStream_t st) {
   const TransposeGeom g = transpose_geom(p);
   if (scratch_bytes < transpose_scratch_bytes(p)) {
@@ -309,6 +398,11 @@ int launch_transpose(const moba_b200_problem& p, const int32_t* block_idx, const
     return MOBA_B200_EUNSUPPORTED;
   }
   int32_t* tiles = static_cast<int32_t*>(scratch);
+  int32_t* slot_counter = reinterpret_cast<int32_t*>(static_cast<unsigned char*>(scratch) + ((tile_count_bytes(p) + 15) & ~size_t(15)));
+  if (sched_items_per_row(p) > 0x7fffffffLL || sched_part_slots(p) > 0x7fffffffLL) {
+    set_error("transpose: chunk_tiles %d cuts the problem into too many work items", sched_chunk_tiles(p));
+    return MOBA_B200_EUNSUPPORTED;
+  }
   const int group = p.q_heads / p.kv_heads;
   const long long capacity = (long long)group * p.max_seqlen * p.slots;
   if (hist_bytes > 48 * 1024) {
@@ -316,7 +410,7 @@ int launch_transpose(const moba_b200_problem& p, const int32_t* block_idx, const
     MOBA_CUDA_OK(cudaFuncSetAttribute(offsets_order_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hist_bytes));
   }
   { KernelTimer t__("count_kernel", st);
-  count_kernel<<<(unsigned)row_ctas, 256, hist_bytes, st>>>(block_idx, cu, tiles, p, g.chunk_rows, g.chunks);
+  count_kernel<<<(unsigned)row_ctas, 256, hist_bytes, st>>>(block_idx, cu, tiles, slot_counter, p, g.chunk_rows, g.chunks);
   MOBA_LAUNCH_OK("count_kernel"); }
   { KernelTimer t__("colscan_kernel", st);
   const unsigned per_row = (unsigned)((p.num_blocks + 3) / 4);
@@ -326,6 +420,15 @@ int launch_transpose(const moba_b200_problem& p, const int32_t* block_idx, const
   offsets_order_kernel<<<dim3(p.n_seq * p.kv_heads, (p.num_blocks + 127) / 128), 1024, hist_bytes, st>>>(
       col_nnz, col_offsets, order, p.num_blocks);
   MOBA_LAUNCH_OK("offsets_order_kernel"); }
+  if (work_items != nullptr) {
+    KernelTimer t__("work_items_kernel", st);
+    unsigned* err = device_error_word();
+    if (err == nullptr) { set_error("transpose: no device error word"); return MOBA_B200_ECUDA; }
+    work_items_kernel<<<p.n_seq * p.kv_heads, 1024, 0, st>>>(col_nnz, order, reinterpret_cast<int4*>(work_items), slot_counter,
+                                                            p.num_blocks, (int)sched_items_per_row(p), sched_chunk_tiles(p),
+                                                            (int)sched_part_slots(p), err);
+    MOBA_LAUNCH_OK("work_items_kernel");
+  }
   { KernelTimer t__("scatter_kernel", st);
   // as many warps per chunk as their cursor arrays leave room for several CTAs per SM
   if (8 * hist_bytes <= 64 * 1024) return launch_scatter<8>(p, block_idx, cu, tiles, col_offsets, rows, heads, slots, g, capacity, st);
@@ -371,7 +474,7 @@ static int static_scratch_address(void** out) {
 
 int launch_transpose_noalloc(const moba_b200_problem& p, const int32_t* block_idx, const int32_t* cu,
                              int32_t* col_nnz, int32_t* col_offsets, int32_t* order, int32_t* rows,
-                             int32_t* heads, int32_t* slots, cudaStream_t st) {
+                             int32_t* heads, int32_t* slots, int32_t* work_items, cudaStream_t st) {
   const size_t need = transpose_scratch_bytes(p);
   if (need > kStaticScratchBytes) {
     set_error("transpose without caller scratch: this problem needs %zu bytes of scratch, the built-in "
@@ -381,9 +484,10 @@ int launch_transpose_noalloc(const moba_b200_problem& p, const int32_t* block_id
   void* scratch = nullptr;
   const int rc = static_scratch_address(&scratch);
   if (rc != MOBA_B200_OK) return rc;
-  // Nothing in the array has to start at zero: the count pass writes every entry the
-  // scan pass reads, so the previous call's contents are simply overwritten.
-  return launch_transpose(p, block_idx, cu, col_nnz, col_offsets, order, rows, heads, slots, scratch,
+  // Nothing in the array has to be cleared by the caller: the count pass writes every entry
+  // the scan pass reads and resets the slot counter, so the previous call's contents are
+  // simply overwritten.
+  return launch_transpose(p, block_idx, cu, col_nnz, col_offsets, order, rows, heads, slots, work_items, scratch,
                           kStaticScratchBytes, st);
 }
 

@@ -26,8 +26,10 @@ def moba_backward(dout, q, k, v, out, lse, part_lse, cfg: MoBAConfig, index: CSC
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     delta = torch.empty((b, hq, s), device=q.device, dtype=torch.float32)
     dq_part = torch.empty((b, hq, s, index.max_slots, d), device=q.device, dtype=q.dtype)
+    # float32 dK/dV partials of the columns the scheduler cut into several work items
+    dkv_scratch = torch.empty((max(16, _lib.load().moba_b200_dkv_scratch_bytes(prob)),), device=q.device, dtype=torch.uint8)
     _lib.call("moba_b200_bwd", q.device, "moba_backward",
               prob, _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(dout), _lib.ptr(lse),
               _lib.ptr(part_lse), index.c_struct(), _lib.ptr(index.cu_seqlens), _lib.ptr(delta),
-              _lib.ptr(dq_part), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv))
+              _lib.ptr(dq_part), _lib.ptr(dkv_scratch), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv))
     return dq, dk, dv

@@ -50,8 +50,11 @@ def _validate(q, k, v, cfg: MoBAConfig, cu_seqlens=None, max_seqlen=None) -> Non
 
 
 def _problem(q, k, cfg, index: CSCIndex, causal=True, part_f32=False):
+    """The problem record of a call that uses `index`: the scheduling chunk size is the one
+    the index's work items were cut with."""
     return _lib.make_problem(tuple(q.shape), k.shape[2], q.dtype, cfg, index.cu_seqlens,
-                             index.max_seqlen, causal=causal, part_f32=part_f32)
+                             index.max_seqlen, causal=causal, part_f32=part_f32,
+                             chunk_tiles=index.chunk_tiles if index.work_items is not None else None)
 
 
 def _check_index(q, k, cfg, index: CSCIndex) -> None:

@@ -23,6 +23,12 @@ class CSCIndex:
     and which of the query's slots the pair owns), order [n_seq,Hkv,nb] (blocks
     by descending col_nnz, stable). All int32. Unlike the reference, entries of
     a column are always ordered by (query head, position).
+
+    `work_items` [n_seq,Hkv,items_per_row,4] (not in the reference) is the dispatch
+    list the persistent tensor-core kernels walk: every column, in `order`, cut into
+    items of at most `chunk_tiles` tiles of 128 queries -- {block, first tile, tiles,
+    dK/dV partial slot | -1 whole column | -2 padding}. An index without it (built by
+    hand) runs on the portable kernels only.
     """
 
     col_nnz: torch.Tensor
@@ -36,12 +42,17 @@ class CSCIndex:
     num_query_heads: int
     cu_seqlens: Optional[torch.Tensor] = None
     max_seqlen: Optional[int] = None
+    work_items: Optional[torch.Tensor] = None
+    chunk_tiles: int = 0
 
     def c_struct(self) -> "_lib.Index":
+        items = self.work_items
         return _lib.Index(self.col_nnz.data_ptr(), self.col_offsets.data_ptr(),
                           self.order.data_ptr(), self.row_indices.data_ptr(),
                           self.head_indices.data_ptr(), self.slot_of_pair.data_ptr(),
-                          self.row_indices.shape[-1])
+                          self.row_indices.shape[-1],
+                          None if items is None else items.data_ptr(),
+                          0 if items is None else items.shape[2], self.chunk_tiles)
 
 
 def build_csc_from_indices(block_idx: torch.Tensor, num_blocks: int, cfg: MoBAConfig,
@@ -75,15 +86,19 @@ def build_csc_from_indices(block_idx: torch.Tensor, num_blocks: int, cfg: MoBACo
     head_indices = torch.empty((n_seq, hkv, cap), **i32)
     slot_of_pair = torch.empty((n_seq, hkv, cap), **i32)
     lib = _lib.load()
+    per_row = lib.moba_b200_work_items_per_row(prob)
+    _lib.check(per_row, "build_csc_from_indices")
+    work_items = torch.empty((n_seq, hkv, per_row, 4), **i32)
     nbytes = lib.moba_b200_transpose_scratch_bytes(prob)
     scratch = torch.empty((max(nbytes, 4),), device=dev, dtype=torch.uint8)
     _lib.call("moba_b200_transpose", dev, "build_csc_from_indices",
               prob, _lib.ptr(block_idx), _lib.ptr(cu_seqlens), _lib.ptr(col_nnz), _lib.ptr(col_offsets),
               _lib.ptr(order), _lib.ptr(row_indices), _lib.ptr(head_indices), _lib.ptr(slot_of_pair),
-              _lib.ptr(scratch), scratch.numel())
+              _lib.ptr(work_items), _lib.ptr(scratch), scratch.numel())
     return CSCIndex(col_nnz, col_offsets, row_indices, head_indices, slot_of_pair, order,
                     num_blocks=num_blocks, max_slots=slots, num_query_heads=hq,
-                    cu_seqlens=cu_seqlens, max_seqlen=max_seqlen)
+                    cu_seqlens=cu_seqlens, max_seqlen=max_seqlen,
+                    work_items=work_items, chunk_tiles=lib.moba_b200_chunk_tiles(prob))
 
 
 def build_csc_fused(q: torch.Tensor, k: torch.Tensor, cfg: MoBAConfig, cu_seqlens=None,
@@ -96,22 +111,29 @@ def build_csc_fused(q: torch.Tensor, k: torch.Tensor, cfg: MoBAConfig, cu_seqlen
 
 
 def csc_to_mask(index: CSCIndex, seq_len: int) -> torch.Tensor:
-    """Expands an index to the dense mask [B|1, Hq, seq_len, nb] the oracle uses
-    (reference: routing.py:564-624). Test support; synchronises."""
-    n_seq, hkv, n = index.col_nnz.shape
-    packed = index.cu_seqlens is not None
+    """Dense view of an index: bool [B|1, Hq, seq_len, nb], True where the query (row of the
+    token axis, head) lists the block (reference: routing.py:564-624, same contract). Test
+    support: it synchronises, and it raises ValueError on an index whose offsets do not
+    tile its pair arrays.
+
+    Every pair of a (sequence, kv head) row is labelled with its block by searching the row's
+    end offsets, so the whole index is expanded with one search and one indexed store."""
+    n_seq, hkv, nb = index.col_nnz.shape
     dev = index.col_nnz.device
-    out = torch.zeros(1 if packed else n_seq, index.num_query_heads, seq_len, n,
-                      dtype=torch.bool, device=dev)
-    prefix = index.col_nnz.cumsum(-1) - index.col_nnz
-    if not torch.equal(prefix.to(index.col_offsets.dtype), index.col_offsets[..., :n]):
+    ends = index.col_offsets[..., 1:].long()                          # [n_seq, Hkv, nb]
+    starts = index.col_offsets[..., :nb].long()
+    if not (torch.equal(ends - starts, index.col_nnz.long()) and bool((starts[..., :1] == 0).all())):
         raise ValueError("col_offsets is not the exclusive prefix sum of col_nnz; the index is inconsistent")
-    cols = torch.arange(n, device=dev)
-    for si in range(n_seq):
-        for kv in range(hkv):
-            blocks = torch.repeat_interleave(cols, index.col_nnz[si, kv].long())
-            total = blocks.numel()
-            rows = index.row_indices[si, kv, :total].long()
-            heads = index.head_indices[si, kv, :total].long()
-            out[0 if packed else si, heads, rows, blocks] = True
+    totals = ends[..., -1]                                            # pairs per row
+    cap = index.row_indices.shape[-1]
+    if int(totals.max()) > cap:
+        raise ValueError(f"the index lists {int(totals.max())} pairs in a row that holds {cap}")
+    slot = torch.arange(cap, device=dev).expand(n_seq, hkv, cap)
+    block = torch.searchsorted(ends.contiguous(), slot.contiguous(), right=True)   # pair -> its block
+    live = slot < totals[..., None]
+    seq = torch.arange(n_seq, device=dev).view(n_seq, 1, 1).expand(n_seq, hkv, cap)
+    batch_row = torch.zeros_like(seq) if index.cu_seqlens is not None else seq
+    out = torch.zeros(1 if index.cu_seqlens is not None else n_seq, index.num_query_heads, seq_len, nb,
+                      dtype=torch.bool, device=dev)
+    out[batch_row[live], index.head_indices.long()[live], index.row_indices.long()[live], block[live]] = True
     return out

@@ -1,11 +1,16 @@
 """Packed (variable-length) batch boundary (reference: src/moba/varlen.py:33-236).
 
 `validate_cu_seqlens` runs on every call and never reads device memory.
-`pack`, `unpack` and `from_nested` build batches and may synchronise once.
+`pack`, `unpack` and `from_nested` build batches: row gathers done by the CUDA
+kernels of csrc/varlen.cu through the C ABI (`moba_b200_pack_index`,
+`moba_b200_pack_rows`, `moba_b200_unpack_rows`, `moba_b200_seq_meta`). `pack`
+and `from_nested` synchronise once, to learn the token total and the longest
+sequence; like every other entry point they take CUDA tensors only.
 """
 
 import torch
-import torch.nn.functional as F
+
+from moba_triton_b200 import _lib
 
 
 def validate_cu_seqlens(cu_seqlens: torch.Tensor, total_tokens: int,
@@ -43,46 +48,76 @@ def validate_cu_seqlens(cu_seqlens: torch.Tensor, total_tokens: int,
     return cu_seqlens.numel() - 1
 
 
+def _row_bytes(x: torch.Tensor) -> int:
+    return x.shape[-2] * x.shape[-1] * x.element_size()
+
+
+def _read_meta(meta: torch.Tensor):
+    """(total tokens, longest sequence): the one host synchronisation of a batch build."""
+    total, longest = meta.tolist()
+    return int(total), int(longest)
+
+
 def pack(x: torch.Tensor, attention_mask: torch.Tensor):
-    """[B,S,H,D] + [B,S] mask -> (packed [1,T,H,D], cu_seqlens int32 [B+1], max_seqlen)."""
+    """[B,S,H,D] + [B,S] mask (nonzero = real token) -> (packed [1,T,H,D], cu_seqlens
+    int32 [B+1] on the device of x, max_seqlen as an int). Kept rows keep their (b, s) order."""
     if x.ndim != 4:
         raise ValueError(f"x must be [B, S, H, D], got {tuple(x.shape)}")
-    b, s = x.shape[:2]
+    b, s, h, d = x.shape
     if tuple(attention_mask.shape) != (b, s):
         raise ValueError(
             f"attention_mask must be [B, S] = {(b, s)}, got {tuple(attention_mask.shape)}")
-    keep = attention_mask.bool()
-    lengths = keep.sum(dim=1, dtype=torch.int32)
-    cu = F.pad(lengths.cumsum(0, dtype=torch.int32), (1, 0))
-    longest = int(lengths.max())
-    bi, si = keep.nonzero(as_tuple=True)
-    return x[bi, si].unsqueeze(0), cu, longest
+    _lib.require_cuda(x, attention_mask)
+    x = x.contiguous()
+    mask = attention_mask.to(x.device)
+    if mask.dtype not in (torch.bool, torch.uint8, torch.int8, torch.int32, torch.int64):
+        mask = mask != 0
+    mask = mask.contiguous()
+    i32 = dict(device=x.device, dtype=torch.int32)
+    dest = torch.empty((b, s), **i32)
+    lengths = torch.empty((b,), **i32)
+    cu = torch.empty((b + 1,), **i32)
+    meta = torch.empty((2,), **i32)
+    _lib.call("moba_b200_pack_index", x.device, "pack", _lib.ptr(mask), mask.element_size(), b, s,
+              _lib.ptr(dest), _lib.ptr(lengths), _lib.ptr(cu), _lib.ptr(meta))
+    total, longest = _read_meta(meta)
+    packed = torch.empty((1, total, h, d), device=x.device, dtype=x.dtype)
+    if total:
+        _lib.call("moba_b200_pack_rows", x.device, "pack", _lib.ptr(x), _lib.ptr(dest), _lib.ptr(cu),
+                  _lib.ptr(packed), b, s, _row_bytes(x))
+    return packed, cu, longest
 
 
 def unpack(packed: torch.Tensor, cu_seqlens: torch.Tensor, batch: int, seq_len: int):
-    """Inverse of `pack`; padding positions come back as zeros."""
+    """Inverse of `pack` for sequences stored from position 0: [1,T,H,D] -> [batch,seq_len,H,D],
+    padding positions zeroed."""
     if packed.ndim != 4 or packed.shape[0] != 1:
         raise ValueError(f"packed must be [1, T, H, D], got {tuple(packed.shape)}")
     if cu_seqlens.numel() != batch + 1:
         raise ValueError(
             f"cu_seqlens has {cu_seqlens.numel()} entries, expected {batch + 1} for batch {batch}")
+    _lib.require_cuda(packed, cu_seqlens)
     _, _, h, d = packed.shape
-    lengths = (cu_seqlens[1:] - cu_seqlens[:-1]).to(torch.int64)
-    keep = torch.arange(seq_len, device=packed.device)[None, :] < lengths[:, None]
-    out = packed.new_zeros(batch, seq_len, h, d)
-    bi, si = keep.nonzero(as_tuple=True)
-    out[bi, si] = packed[0]
+    packed = packed.contiguous()
+    cu = cu_seqlens.to(device=packed.device, dtype=torch.int32).contiguous()
+    out = torch.empty((batch, seq_len, h, d), device=packed.device, dtype=packed.dtype)
+    _lib.call("moba_b200_unpack_rows", packed.device, "unpack", _lib.ptr(packed), _lib.ptr(cu), _lib.ptr(out),
+              batch, seq_len, _row_bytes(packed))
     return out
 
 
 def from_nested(nt: torch.Tensor):
-    """Jagged nested tensor [B, j, H, D] -> (packed, cu_seqlens, max_seqlen)."""
+    """Jagged nested tensor [B, j, H, D] -> (packed, cu_seqlens, max_seqlen). Its values are
+    the packed rows already and its offsets are cu_seqlens; only max_seqlen is computed."""
     if not nt.is_nested:
         raise ValueError("from_nested expects a nested tensor")
     values = nt.values()
     if values.ndim != 3:
         raise ValueError(
             f"expected a [B, j, H, D] jagged tensor; its values are {tuple(values.shape)}")
-    offsets = nt.offsets()
-    longest = int((offsets[1:] - offsets[:-1]).max())
-    return values.unsqueeze(0).contiguous(), offsets.to(torch.int32), longest
+    _lib.require_cuda(values)
+    cu = nt.offsets().to(device=values.device, dtype=torch.int32).contiguous()
+    meta = torch.empty((2,), device=values.device, dtype=torch.int32)
+    _lib.call("moba_b200_seq_meta", values.device, "from_nested", _lib.ptr(cu), cu.numel() - 1, _lib.ptr(meta))
+    _, longest = _read_meta(meta)
+    return values.contiguous().unsqueeze(0), cu, longest

@@ -268,8 +268,10 @@ def test_determinism_causality_and_block_perturbation(device, kernel_path):
     b = _grads(q, k, v, cfg, index, do)
     for x, y in zip(a, b):
         assert torch.equal(x, y), "repeated runs differ"
-    # dispatch order is irrelevant (doubles as a write-race detector)
-    flipped = dataclasses.replace(index, order=index.order.flip(-1).contiguous())
+    # dispatch order is irrelevant (doubles as a write-race detector): the portable kernels walk
+    # `order`, the tensor-core kernels the work items
+    flipped = dataclasses.replace(index, order=index.order.flip(-1).contiguous(),
+                                  work_items=index.work_items.flip(2).contiguous())
     for x, y in zip(a, _grads(q, k, v, cfg, flipped, do)):
         assert torch.equal(x, y), "results depend on the dispatch order"
     # perturbing one block's values changes exactly the queries that selected it

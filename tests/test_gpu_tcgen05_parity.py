@@ -178,3 +178,70 @@ def test_non_causal_own_block_on_tensor_cores(d, device):
 def test_float16_on_tensor_cores(d, device):
     cfg = moba.MoBAConfig(128, 8, dtype=torch.float16)
     _check_op((1, 2048, 4, d), 2, torch.float16, cfg, device, seed=11)
+
+
+# ---------------------------------------------------------------------------
+# the scheduler's column splitting
+# ---------------------------------------------------------------------------
+
+@pytest.fixture
+def tiny_chunks():
+    old = _lib.set_chunk_tiles(1)                      # every column of two or more tiles is cut
+    yield
+    _lib.set_chunk_tiles(old)
+
+
+def _work_item_invariants(index):
+    nnz = index.col_nnz.cpu()
+    items = index.work_items.cpu()
+    n_seq, hkv, nb = nnz.shape
+    slots_seen = set()
+    for si in range(n_seq):
+        for h in range(hkv):
+            it = items[si, h]
+            it = it[it[:, 3] != -2]                        # drop the padding
+            covered = torch.zeros(nb, dtype=torch.int64)
+            for blk, tile0, tiles, slot in it.tolist():
+                total = -(-int(nnz[si, h, blk]) // 128)
+                assert tile0 == covered[blk], "the items of a column must follow one another"
+                covered[blk] += tiles
+                assert tiles <= index.chunk_tiles and (tiles > 0 or total == 0)
+                if slot >= 0:
+                    assert total > index.chunk_tiles and slot not in slots_seen
+                    slots_seen.add(slot)
+                else:
+                    assert total <= index.chunk_tiles
+            assert torch.equal(covered, -(-nnz[si, h].long() // 128)), "every tile of every column exactly once"
+            # dispatch order: heaviest column first
+            first_items = it[it[:, 1] == 0][:, 0].long()
+            assert torch.equal(first_items, index.order[si, h].cpu().long())
+    return len(slots_seen)
+
+
+@pytest.mark.parametrize("d,hq,hkv,cu", [(64, 4, 2, None), (128, 4, 1, None), (64, 4, 2, [0, 640, 1000, 1664])],
+                         ids=["d64", "d128-gqa4", "d64-packed"])
+def test_split_columns_give_the_same_results(d, hq, hkv, cu, device, tiny_chunks):
+    """With one-tile work items every crowded column is split: forward partials and dQ do not
+    depend on the cut (bitwise equal to the unsplit run), dK/dV are sums of float32 partials
+    (equal to the oracle within tolerance, and the same bits on every run)."""
+    cfg = moba.MoBAConfig(128, 4)
+    t = 2048 if cu is None else cu[-1]
+    shape = (1, t, hq, d)
+    (qd, kd, vd, dod), got, index = _check_op(shape, hkv, torch.bfloat16, cfg, device, cu=cu, seed=51)
+    assert index.chunk_tiles == 1
+    assert _work_item_invariants(index) > 0, "no column was split, nothing is being checked"
+    kw = {} if cu is None else dict(cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=device),
+                                    max_seqlen=max(b - a for a, b in zip(cu[:-1], cu[1:])))
+    again = _grads(qd, kd, vd, cfg, dod, index=index)
+    for a, b in zip(got, again):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16)), "split runs must be reproducible"
+    old = _lib.set_chunk_tiles(1 << 20)                # no column is that long: nothing is cut
+    try:
+        whole_index = moba.build_csc_fused(qd, kd, cfg, **kw)
+        assert _work_item_invariants(whole_index) == 0
+        whole = _grads(qd, kd, vd, cfg, dod, index=whole_index)
+    finally:
+        _lib.set_chunk_tiles(old)
+    assert torch.equal(got[0], whole[0]) and torch.equal(got[1], whole[1])
+    assert torch.allclose(got[2].float(), whole[2].float(), rtol=2e-2, atol=2e-3)
+    assert torch.allclose(got[3].float(), whole[3].float(), rtol=2e-2, atol=2e-3)

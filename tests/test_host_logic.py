@@ -65,18 +65,23 @@ def test_cu_seqlens_validation():
         validate_cu_seqlens(ok, 128, 64)
 
 
-def test_pack_unpack_round_trip_and_nested():
-    g = torch.Generator().manual_seed(0)
-    x = torch.randn(3, 10, 2, 4, generator=g)
-    lens = [10, 3, 7]
-    mask = torch.arange(10)[None, :] < torch.tensor(lens)[:, None]
-    packed, cu, longest = pack(x, mask)
-    assert packed.shape == (1, 20, 2, 4) and cu.tolist() == [0, 10, 13, 20] and longest == 10
-    back = unpack(packed, cu, 3, 10)
-    assert torch.equal(back, x * mask[:, :, None, None])
-    nt = torch.nested.nested_tensor([x[i, :n] for i, n in enumerate(lens)], layout=torch.jagged)
-    p2, cu2, l2 = from_nested(nt)
-    assert torch.equal(p2, packed) and cu2.tolist() == cu.tolist() and l2 == 10
+def test_pack_and_unpack_check_shapes_and_refuse_cpu_tensors():
+    x = torch.zeros(3, 10, 2, 4)
+    mask = torch.ones(3, 10, dtype=torch.bool)
+    with pytest.raises(ValueError, match=r"\[B, S, H, D\]"):
+        pack(x[0], mask)
+    with pytest.raises(ValueError, match="attention_mask"):
+        pack(x, mask[:, :5])
+    with pytest.raises(ValueError, match=r"\[1, T, H, D\]"):
+        unpack(x, torch.tensor([0, 10], dtype=torch.int32), 1, 10)
+    with pytest.raises(ValueError, match="entries"):
+        unpack(x[:1], torch.tensor([0, 10], dtype=torch.int32), 3, 10)
+    with pytest.raises(ValueError, match="nested"):
+        from_nested(x)
+    with pytest.raises(RuntimeError, match="no CPU path"):          # the row gathers are CUDA kernels
+        pack(x, mask)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        unpack(x[:1], torch.tensor([0, 10], dtype=torch.int32), 1, 10)
 
 
 def test_product_refuses_cpu_tensors_instead_of_falling_back():
@@ -107,7 +112,16 @@ def test_c_abi_rejects_bad_problems_without_touching_a_gpu():
     prob = _lib.make_problem((1, 64, 2, 64), 2, torch.bfloat16, cfg)
     assert lib.moba_b200_pool(prob, None, None, None, None) == -1
     assert b"NULL" in lib.moba_b200_last_error()
-    assert lib.moba_b200_transpose_scratch_bytes(prob) == 1 * 2 * 2 * 1 * 1 * 4
+    assert lib.moba_b200_transpose_scratch_bytes(prob) == 1 * 2 * 2 * 1 * 1 * 4 + 16   # histograms + slot counter
+    # scheduling sizes are functions of the problem record alone
+    assert lib.moba_b200_chunk_tiles(prob) == 8                       # small problems: the floor
+    pairs = 1 * 64 * 2 * 4
+    assert lib.moba_b200_work_items_per_row(prob) == 2 + pairs // (128 * 8) + 1
+    assert lib.moba_b200_dkv_scratch_bytes(prob) == (2 * (pairs // (128 * 8) + 1) + 1) * 2 * 128 * 64 * 4
+    big = _lib.make_problem((1, 524288, 32, 128), 8, torch.bfloat16, moba.MoBAConfig(128, 8))
+    assert lib.moba_b200_chunk_tiles(big) == -(-(524288 * 32 * 8 // 128) // (4 * 148))
+    assert lib.moba_b200_work_items_per_row(big) <= 4096 + 4 * 148 + 1
+    assert _lib.make_problem((1, 64, 2, 64), 2, torch.bfloat16, cfg, chunk_tiles=3).chunk_tiles == 3
 
 
 def test_product_never_imports_the_oracle():
@@ -149,3 +163,36 @@ def test_a_swapped_exact_tie_is_not_accepted_as_a_near_tie():
     assert near_tie_report(engine, oracle, scores, 8) == (1, 1)
     scores[..., 1] = 1.0 - 2.0 ** -8                         # one rounding step apart: a near tie
     assert near_tie_report(engine, oracle, scores, 8) == (1, 0)
+
+
+def test_bench_rows_have_the_reference_columns_and_closed_form_sparsity(tmp_path):
+    """Column names and order of the reference's BenchRow (bench/suite.py:37-63); pair counts
+    against real selection masks (as tests/test_bench.py:66-92 does there)."""
+    import csv
+    from moba_triton_b200 import bench_rows as br
+    from oracle import moba_oracle as orc
+    assert br.COLUMNS == (
+        "backend", "batch", "heads", "seq_len", "head_dim", "block_size", "top_k", "dtype", "latency_ms", "tflops",
+        "peak_memory_mb", "sparsity", "speedup_vs_dense", "speedup_ceiling", "attainment", "gpu_name", "capability",
+        "total_memory_mb", "torch_version", "triton_version", "cuda_version", "status", "note")
+    for s, bs, top_k in ((512, 64, 3), (200, 32, 4), (4096, 128, 8)):
+        cfg = moba.MoBAConfig(bs, top_k)
+        assert br.attended_pairs(s, cfg) == orc.attended_pairs(s, bs, top_k)
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(1, 200, 1, 64, generator=g)
+    cfg = moba.MoBAConfig(32, 3)
+    mask = orc.selection_mask(q, q, 32, 3)[0, 0]                             # [S, nb]
+    pos = torch.arange(200)
+    visible = mask[:, pos // 32] & (pos[None, :] <= pos[:, None])
+    assert int(visible.sum()) == br.attended_pairs(200, cfg)
+    row = br.make_row("ours_b200", (1, 4096, 4, 64), moba.MoBAConfig(128, 8), 0.05, 12.0, dense_latency_ms=0.2)
+    assert tuple(row) == br.COLUMNS and row["status"] == "ok"
+    assert abs(row["speedup_vs_dense"] - 4.0) < 1e-12 and abs(row["attainment"] - 4.0 * row["sparsity"]) < 1e-12
+    assert abs(row["tflops"] - 4.0 * 4 * br.attended_pairs(4096, moba.MoBAConfig(128, 8)) * 64 / 0.05e-3 / 1e12) < 1e-9
+    bad = br.make_row("ours_b200", (1, 4096, 4, 64), moba.MoBAConfig(128, 8), float("nan"), float("nan"),
+                      status="error", note="x" * 500)
+    assert bad["latency_ms"] != bad["latency_ms"] and len(bad["note"]) == 160
+    path = tmp_path / "rows.csv"
+    br.write_csv(str(path), [row, bad])
+    got = list(csv.DictReader(open(path)))
+    assert list(got[0]) == list(br.COLUMNS) and got[1]["status"] == "error"

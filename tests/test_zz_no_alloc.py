@@ -22,10 +22,12 @@ pytestmark = pytest.mark.gpu
 def _transpose(noalloc, prob, block_idx, cu, hkv, nb, cap, n_seq, dev):
     i32 = dict(device=dev, dtype=torch.int32)
     # poisoned outputs: everything that matters must be written by the call
+    lib = _lib.load()
+    per_row = lib.moba_b200_work_items_per_row(prob)
     outs = [torch.full((n_seq, hkv, nb), -7, **i32), torch.full((n_seq, hkv, nb + 1), -7, **i32),
             torch.full((n_seq, hkv, nb), -7, **i32), torch.full((n_seq, hkv, cap), -7, **i32),
-            torch.full((n_seq, hkv, cap), -7, **i32), torch.full((n_seq, hkv, cap), -7, **i32)]
-    lib = _lib.load()
+            torch.full((n_seq, hkv, cap), -7, **i32), torch.full((n_seq, hkv, cap), -7, **i32),
+            torch.full((n_seq, hkv, per_row, 4), -7, **i32)]
     args = [prob, _lib.ptr(block_idx), _lib.ptr(cu)] + [_lib.ptr(t) for t in outs]
     if noalloc:
         rc = lib.moba_b200_transpose_noalloc(*args, _lib.stream_ptr(dev))
@@ -70,8 +72,11 @@ def test_noalloc_transpose_matches_the_caller_scratch_entry_point(shape, hkv, bs
         for si in range(n_seq):
             for h in range(hkv):
                 n = int(totals[si, h])
-                for name, g, w in zip(("row_indices", "head_indices", "slot_of_pair"), got[3:], want[3:]):
+                for name, g, w in zip(("row_indices", "head_indices", "slot_of_pair"), got[3:6], want[3:6]):
                     assert torch.equal(g[si, h, :n], w[si, h, :n]), f"{name} differs on call {attempt + 1}"
+        # work items: same cuts; partial-slot numbers only name scratch memory and may differ
+        assert torch.equal(got[6][..., :3], want[6][..., :3]), f"work items differ on call {attempt + 1}"
+        assert torch.equal(got[6][..., 3].clamp(max=0), want[6][..., 3].clamp(max=0))
 
 
 def test_noalloc_transpose_refuses_problems_beyond_its_built_in_scratch(device):
@@ -82,7 +87,7 @@ def test_noalloc_transpose_refuses_problems_beyond_its_built_in_scratch(device):
     assert lib.moba_b200_transpose_scratch_bytes(prob) > 8 << 20
     dummy = torch.zeros(16, device=device, dtype=torch.int32)
     p = _lib.ptr(dummy)
-    rc = lib.moba_b200_transpose_noalloc(prob, p, None, p, p, p, p, p, p, _lib.stream_ptr(device))
+    rc = lib.moba_b200_transpose_noalloc(prob, p, None, p, p, p, p, p, p, p, _lib.stream_ptr(device))
     assert rc == -2
     assert b"built-in" in lib.moba_b200_last_error()
 
@@ -99,9 +104,10 @@ def test_noalloc_transpose_leaves_device_memory_untouched(device):
     prob = _lib.make_problem(shape, hkv, torch.bfloat16, cfg)
     nb, cap = kbar.shape[2], (shape[2] // hkv) * shape[1] * cfg.slots_per_query
     i32 = dict(device=device, dtype=torch.int32)
-    outs = [torch.empty((1, hkv, nb), **i32), torch.empty((1, hkv, nb + 1), **i32), torch.empty((1, hkv, nb), **i32),
-            torch.empty((1, hkv, cap), **i32), torch.empty((1, hkv, cap), **i32), torch.empty((1, hkv, cap), **i32)]
     lib = _lib.load()
+    outs = [torch.empty((1, hkv, nb), **i32), torch.empty((1, hkv, nb + 1), **i32), torch.empty((1, hkv, nb), **i32),
+            torch.empty((1, hkv, cap), **i32), torch.empty((1, hkv, cap), **i32), torch.empty((1, hkv, cap), **i32),
+            torch.empty((1, hkv, lib.moba_b200_work_items_per_row(prob), 4), **i32)]
     args = [prob, _lib.ptr(block_idx), None] + [_lib.ptr(t) for t in outs] + [_lib.stream_ptr(device)]
     _lib.check(lib.moba_b200_transpose_noalloc(*args), "transpose")      # first call on this device
     torch.cuda.synchronize()
