@@ -122,6 +122,29 @@ int moba_b200_device_status(unsigned int* word, void* stream);
  * for this problem, or a negative error code. */
 int moba_b200_path_for(const moba_b200_problem* p, int stage);
 
+/* The launch table: everything the library decides per problem, looked up in
+ * constant time from the problem record (no measurement, no device query).
+ * The tensor-core kernels have one tile plan per head_dim; the transpose and
+ * the scheduler size themselves by sequence length and pair count. Choices
+ * never depend on whether the batch is packed, so a packed batch and its
+ * sequences run alone go through the same kernels and give the same bits.
+ * Stands in for the reference's table lookup (src/moba/kernels/tuning.py:335-409,
+ * tuned_configs.py:87-285), whose autotuner has no counterpart here. */
+typedef struct moba_b200_plan {
+  int32_t gate_path, fwd_path, bwd_path;   /* MOBA_B200_PATH_* of each stage */
+  int32_t fwd_tiles_in_flight;             /* forward: 128-query tiles (TMEM buffers, softmax warpgroups) per SM */
+  int32_t fwd_q_stages;                    /* forward: shared-memory stages of gathered Q */
+  int32_t bwd_kv_buffers;                  /* backward: K/V buffers per SM */
+  int32_t bwd_gather_stages;               /* backward: stages of gathered Q and dO */
+  int32_t gate_slots, gate_step;           /* gate: per-thread buffer slots; scores tested between room checks */
+  int32_t transpose_chunk_rows;            /* transpose: rows per histogram chunk */
+  int32_t transpose_chunks;                /*            chunks per sequence */
+  int32_t scatter_warps;                   /*            runs walked side by side per chunk */
+  int32_t chunk_tiles;                     /* scheduler: tiles per work item */
+  int32_t work_items_per_row;              /*            table entries per (sequence, kv head) */
+} moba_b200_plan;
+int moba_b200_launch_plan(const moba_b200_problem* p, moba_b200_plan* plan);
+
 /* Bytes of scratch moba_b200_transpose needs for this problem. */
 size_t moba_b200_transpose_scratch_bytes(const moba_b200_problem* p);
 

@@ -28,6 +28,7 @@ EXPORTS = (
     "moba_b200_device_status", "moba_b200_transpose_noalloc",
     "moba_b200_pack_index", "moba_b200_pack_rows", "moba_b200_unpack_rows", "moba_b200_seq_meta",
     "moba_b200_chunk_tiles", "moba_b200_work_items_per_row", "moba_b200_dkv_scratch_bytes",
+    "moba_b200_launch_plan",
 )
 
 
@@ -43,6 +44,13 @@ class Index(Structure):
                 ("row_indices", c_void_p), ("head_indices", c_void_p),
                 ("slot_of_pair", c_void_p), ("capacity", c_int64),
                 ("work_items", c_void_p), ("items_per_row", c_int32), ("chunk_tiles", c_int32)]
+
+
+class Plan(Structure):
+    _fields_ = [(n, c_int32) for n in (
+        "gate_path", "fwd_path", "bwd_path", "fwd_tiles_in_flight", "fwd_q_stages", "bwd_kv_buffers",
+        "bwd_gather_stages", "gate_slots", "gate_step", "transpose_chunk_rows", "transpose_chunks",
+        "scatter_warps", "chunk_tiles", "work_items_per_row")]
 
 
 _lib = None
@@ -68,6 +76,7 @@ def load():
     lib.moba_b200_gate.argtypes = [P, vp, vp, vp, vp, vp]
     lib.moba_b200_transpose.argtypes = [P, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, c_size_t, vp]
     lib.moba_b200_transpose_noalloc.argtypes = [P, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+    lib.moba_b200_launch_plan.argtypes = [P, POINTER(Plan)]
     lib.moba_b200_chunk_tiles.argtypes = [P]
     lib.moba_b200_work_items_per_row.argtypes = [P]
     lib.moba_b200_dkv_scratch_bytes.argtypes = [P]

@@ -170,6 +170,25 @@ int moba_b200_path_for(const moba_b200_problem* p, int stage) {
   return MOBA_B200_EINVAL;
 }
 
+int moba_b200_launch_plan(const moba_b200_problem* p, moba_b200_plan* plan) {
+  MOBA_TRY(check_problem(p));
+  if (plan == nullptr) { set_error("plan is NULL"); return MOBA_B200_EINVAL; }
+  memset(plan, 0, sizeof(*plan));
+  plan->gate_path = pick(*p, gate_sm100_supported(*p), "gate");
+  plan->fwd_path = pick(*p, fwd_sm100_supported(*p), "forward");
+  plan->bwd_path = pick(*p, bwd_sm100_supported(*p), "backward");
+  if (plan->gate_path < 0 || plan->fwd_path < 0 || plan->bwd_path < 0) return MOBA_B200_EUNSUPPORTED;
+  const TensorCorePlan& t = tensor_core_plan(p->head_dim);
+  if (plan->fwd_path == MOBA_B200_PATH_TCGEN05) { plan->fwd_tiles_in_flight = t.fwd_tiles_in_flight; plan->fwd_q_stages = t.fwd_q_stages; }
+  if (plan->bwd_path == MOBA_B200_PATH_TCGEN05) { plan->bwd_kv_buffers = t.bwd_kv_buffers; plan->bwd_gather_stages = t.bwd_gather_stages; }
+  if (plan->gate_path == MOBA_B200_PATH_TCGEN05) { plan->gate_slots = t.gate_slots; plan->gate_step = t.gate_step; }
+  transpose_plan(*p, &plan->transpose_chunk_rows, &plan->transpose_chunks, &plan->scatter_warps);
+  plan->chunk_tiles = sched_chunk_tiles(*p);
+  const long long per_row = sched_items_per_row(*p);
+  plan->work_items_per_row = per_row > 0x7fffffffLL ? -1 : (int)per_row;
+  return MOBA_B200_OK;
+}
+
 size_t moba_b200_transpose_scratch_bytes(const moba_b200_problem* p) {
   if (check_problem(p) != MOBA_B200_OK) return 0;
   return transpose_scratch_bytes(*p);

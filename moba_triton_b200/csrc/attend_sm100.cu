@@ -43,10 +43,10 @@ template <int D> struct FwdCfg {
   static constexpr int kSubs = D / 64;                 // sub-tiles per operand along the head dim
   static constexpr int kOperand = kSubs * kSub;        // bytes of K, V or one Q stage
   // Tiles in flight (TMEM / P buffers, softmax warpgroups).
-  static constexpr int kBufs = (D == 64) ? 4 : 2;
+  static constexpr int kBufs = tensor_core_plan(D).fwd_tiles_in_flight;
   // Q stages form a ring over the CTA's tile sequence (tile t lives in stage t mod kQStages);
   // shared memory has no room for one stage per buffer at head_dim 64.
-  static constexpr int kQStages = (D == 64) ? 3 : 2;
+  static constexpr int kQStages = tensor_core_plan(D).fwd_q_stages;
   static constexpr int kPBytes = 2 * kSub;             // [128][128] 16-bit
   static constexpr int kSmemData = 2 * kOperand + kQStages * kOperand + kBufs * kPBytes;
   static constexpr int kSmem = kSmemData + 1024 /*align*/ + 10240 /*barriers, row tables*/;

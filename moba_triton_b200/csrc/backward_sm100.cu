@@ -34,8 +34,8 @@ constexpr int kThreads = (kElemWarps + 6) * 32;
 template <int D> struct BwdCfg {
   static constexpr int kSubs = D / 64;
   static constexpr int kOperand = kSubs * kSub;          // K, V, one Q stage, one dO stage
-  static constexpr int kStages = (D == 64) ? 2 : 1;      // Q / dO gather stages
-  static constexpr int kKvBufs = (D == 64) ? 2 : 1;
+  static constexpr int kStages = tensor_core_plan(D).bwd_gather_stages;   // Q / dO gather stages
+  static constexpr int kKvBufs = tensor_core_plan(D).bwd_kv_buffers;
   static constexpr int kPBytes = 2 * kSub;
   // At head_dim 64 there is room for a staging tile of dQ of its own, so dQ can be the first
   // of a tile's last three MMAs and be written out while dV and dK run; at 128 it is staged
@@ -565,16 +565,18 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
 #endif
 }
 
-// dK / dV of the columns that were cut into several work items: one CTA per work item; the
-// CTA of a split column's first item adds the column's float32 partials in item order and
-// stores the result, every other CTA leaves at once.
+// dK / dV of the columns that were cut into several work items. The CTAs walk the work
+// items; at the first item of a split column a CTA adds the column's float32 partials in
+// item order and stores the result. Few columns are split (often none), so a CTA mostly
+// reads 16 bytes per item and moves on.
 template <int D, typename T>
 __global__ void __launch_bounds__(256)
 dkv_reduce_kernel(const float* __restrict__ dkv_scratch, moba_b200_index ix, const int32_t* __restrict__ cu,
-                  T* __restrict__ dk, T* __restrict__ dv, moba_b200_problem p, int n_kv_rows) {
-  const int kv_row = blockIdx.x % n_kv_rows, j = blockIdx.x / n_kv_rows;
+                  T* __restrict__ dk, T* __restrict__ dv, moba_b200_problem p, int n_kv_rows, int n_items) {
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+  const int kv_row = item % n_kv_rows, j = item / n_kv_rows;
   const int4 it = __ldg(reinterpret_cast<const int4*>(ix.work_items) + (size_t)kv_row * ix.items_per_row + j);
-  if (it.w < 0 || it.y != 0) return;                     // not the first item of a split column
+  if (it.w < 0 || it.y != 0) continue;                   // not the first item of a split column
   const int nnz = ix.col_nnz[(size_t)kv_row * p.num_blocks + it.x];
   const int tiles = (nnz + kTile - 1) / kTile;
   const int n_chunks = (tiles + ix.chunk_tiles - 1) / ix.chunk_tiles;
@@ -599,6 +601,7 @@ dkv_reduce_kernel(const float* __restrict__ dkv_scratch, moba_b200_index ix, con
     w.y = pack2<T>(acc.z, acc.w);
     *reinterpret_cast<uint2*>(dst) = w;
   }
+  }
 }
 
 template <int D, typename T>
@@ -619,7 +622,8 @@ int launch_one(const moba_b200_problem& p, const CUtensorMap& km, const CUtensor
     MOBA_LAUNCH_OK("bwd_sm100_kernel");
   }
   KernelTimer timer__("dkv_reduce_kernel", st);
-  dkv_reduce_kernel<D, T><<<n_items, 256, 0, st>>>(dkv_scratch, ix, cu, (T*)dk, (T*)dv, p, p.n_seq * p.kv_heads);
+  dkv_reduce_kernel<D, T><<<n_items < 4 * sms ? n_items : 4 * sms, 256, 0, st>>>(dkv_scratch, ix, cu, (T*)dk, (T*)dv, p,
+                                                                                 p.n_seq * p.kv_heads, n_items);
   MOBA_LAUNCH_OK("dkv_reduce_kernel");
   return MOBA_B200_OK;
 }

@@ -90,6 +90,25 @@ __device__ __forceinline__ SeqSpan seq_span(const int32_t* cu, int packed, int s
   return s;
 }
 
+// ---- launch table of the tensor-core kernels: one tile plan per head_dim ----
+// The kernels take their compile-time constants from this table, and moba_b200_launch_plan
+// reports it, so there is one place that says what runs. Shared memory decides the entries:
+// at head_dim 64 four tiles, three Q stages and double-buffered K/V fit beside the P
+// buffers; at 128 every operand is twice as large.
+struct TensorCorePlan {
+  int head_dim;
+  int fwd_tiles_in_flight, fwd_q_stages;
+  int bwd_kv_buffers, bwd_gather_stages;
+  int gate_slots, gate_step;
+};
+constexpr TensorCorePlan kTensorCorePlans[2] = {
+    {64, 4, 3, 2, 2, 16, 8},
+    {128, 2, 2, 1, 1, 7, 4},
+};
+constexpr const TensorCorePlan& tensor_core_plan(int head_dim) { return kTensorCorePlans[head_dim == 64 ? 0 : 1]; }
+
+void transpose_plan(const moba_b200_problem& p, int* chunk_rows, int* chunks, int* scatter_warps);
+
 // ---- scheduling: columns are dispatched as work items of at most chunk_tiles tiles ----
 // Sizes are fixed functions of the problem record, so that the caller can allocate the
 // item table and the dK/dV partial slots without reading anything back from the device.

@@ -54,8 +54,8 @@ template <int D> struct GateCfg {
   // Per-thread buffer of scores that passed the entry test, in slots of 8 bytes, and how
   // many columns are tested between two checks for room. Two CTAs share an SM, which at
   // head_dim 128 leaves room for 7 slots only.
-  static constexpr int kCap = (D == 64) ? 16 : 7;
-  static constexpr int kStep = (D == 64) ? 8 : 4;
+  static constexpr int kCap = tensor_core_plan(D).gate_slots;
+  static constexpr int kStep = tensor_core_plan(D).gate_step;
   static constexpr int kBufBytes = kCap * kTile * 8;                       // per warpgroup
   static constexpr int kSmem = 3 * kOperand + 2 * kBufBytes + 1024 + 512;  // Q + two Kbar stages + buffers
 };

@@ -363,6 +363,18 @@ scatter_kernel(const int32_t* __restrict__ block_idx, const int32_t* __restrict_
   }
 }
 
+// warps per scatter CTA: as many runs side by side as their cursor arrays leave room for
+static inline int scatter_warps_for(const moba_b200_problem& p) {
+  const size_t hist_bytes = (size_t)p.num_blocks * sizeof(int);
+  if (8 * hist_bytes <= 64 * 1024) return 8;
+  if (4 * hist_bytes <= 200 * 1024) return 4;
+  return 1;
+}
+void transpose_plan(const moba_b200_problem& p, int* chunk_rows, int* chunks, int* scatter_warps) {
+  const TransposeGeom g = transpose_geom(p);
+  *chunk_rows = g.chunk_rows; *chunks = g.chunks; *scatter_warps = scatter_warps_for(p);
+}
+
 template <int W>
 static int launch_scatter(const moba_b200_problem& p, const int32_t* block_idx, const int32_t* cu,
                           const int32_t* tiles, const int32_t* col_offsets, int32_t* rows, int32_t* heads,
@@ -430,9 +442,9 @@ int launch_transpose(const moba_b200_problem& p, const int32_t* block_idx, const
     MOBA_LAUNCH_OK("work_items_kernel");
   }
   { KernelTimer t__("scatter_kernel", st);
-  // as many warps per chunk as their cursor arrays leave room for several CTAs per SM
-  if (8 * hist_bytes <= 64 * 1024) return launch_scatter<8>(p, block_idx, cu, tiles, col_offsets, rows, heads, slots, g, capacity, st);
-  if (4 * hist_bytes <= 200 * 1024) return launch_scatter<4>(p, block_idx, cu, tiles, col_offsets, rows, heads, slots, g, capacity, st);
+  const int w = scatter_warps_for(p);
+  if (w == 8) return launch_scatter<8>(p, block_idx, cu, tiles, col_offsets, rows, heads, slots, g, capacity, st);
+  if (w == 4) return launch_scatter<4>(p, block_idx, cu, tiles, col_offsets, rows, heads, slots, g, capacity, st);
   return launch_scatter<1>(p, block_idx, cu, tiles, col_offsets, rows, heads, slots, g, capacity, st); }
 }
 

@@ -196,3 +196,31 @@ def test_bench_rows_have_the_reference_columns_and_closed_form_sparsity(tmp_path
     br.write_csv(str(path), [row, bad])
     got = list(csv.DictReader(open(path)))
     assert list(got[0]) == list(br.COLUMNS) and got[1]["status"] == "error"
+
+
+def test_launch_plan_is_a_table_lookup_on_the_problem_record():
+    from moba_triton_b200.tuning import launch_plan
+    cfg = moba.MoBAConfig(128, 8)
+    target = launch_plan((1, 131072, 4, 64), 4, torch.bfloat16, cfg)
+    assert target["gate_path"] == target["fwd_path"] == target["bwd_path"] == "tcgen05"
+    assert (target["fwd_tiles_in_flight"], target["fwd_q_stages"]) == (4, 3)
+    assert (target["bwd_kv_buffers"], target["bwd_gather_stages"]) == (2, 2)
+    assert (target["gate_slots"], target["gate_step"]) == (16, 8)
+    assert (target["transpose_chunk_rows"], target["transpose_chunks"], target["scatter_warps"]) == (512, 256, 8)
+    assert target["chunk_tiles"] == -(-(131072 * 4 * 8 // 128) // (4 * 148))
+    gqa = launch_plan((1, 524288, 32, 128), 8, torch.bfloat16, cfg)
+    assert (gqa["fwd_tiles_in_flight"], gqa["fwd_q_stages"], gqa["bwd_kv_buffers"], gqa["gate_slots"]) == (2, 2, 1, 7)
+    assert gqa["scatter_warps"] == 4 and gqa["transpose_chunk_rows"] == 2048
+    # float32 and odd block sizes run the portable kernels; the tile plan is then empty
+    slow = launch_plan((1, 4096, 4, 64), 4, torch.float32, moba.MoBAConfig(128, 8, dtype=torch.float32))
+    assert slow["fwd_path"] == "portable" and slow["fwd_tiles_in_flight"] == 0
+    assert launch_plan((1, 4096, 4, 64), 4, torch.bfloat16, moba.MoBAConfig(64, 4))["gate_path"] == "portable"
+    # packed or padded, the same sequence length gets the same kernels (bitwise packed == alone)
+    cu = torch.tensor([0, 1000, 2024], dtype=torch.int32)
+    packed = launch_plan((1, 2024, 4, 64), 2, torch.bfloat16, cfg, cu_seqlens=cu, max_seqlen=1024)
+    alone = launch_plan((1, 1024, 4, 64), 2, torch.bfloat16, cfg)
+    for key in ("gate_path", "fwd_path", "bwd_path", "fwd_tiles_in_flight", "fwd_q_stages", "bwd_kv_buffers",
+                "bwd_gather_stages", "gate_slots", "gate_step"):
+        assert packed[key] == alone[key]
+    with pytest.raises(ValueError):
+        launch_plan((1, 64, 3, 64), 2, torch.bfloat16, cfg)
