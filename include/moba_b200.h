@@ -19,9 +19,11 @@
  *   col_nnz, order        [n_seq, Hkv, num_blocks]   int32
  *   col_offsets           [n_seq, Hkv, num_blocks+1] int32
  *   row/head/slot arrays  [n_seq, Hkv, capacity]     int32,
- *                         capacity = (Hq/Hkv) * max_seqlen * slots
+ *                         capacity = (Hq/Hkv) * max_seqlen * slots (win_rows in place
+ *                         of max_seqlen when the problem names a query window)
  *   work_items            [n_seq, Hkv, items_per_row, 4]  int32
- *   part_o                [B, Hq, S, slots, D]  (dtype of q, or float32)
+ *   part_o                [B, Hq, S, slots, D]  (dtype of q, or float32); S -> win_rows
+ *                         when the problem names a query window
  *   part_lse, dq marker   [B, Hq, S, slots]     float32, log2 units, -inf = unwritten
  *   lse, delta            [B, Hq, S]            float32 (lse in log2 units)
  *   dq_part               [B, Hq, S, slots, D]  dtype of q
@@ -75,6 +77,10 @@ typedef struct moba_b200_problem {
   int32_t part_f32;       /* 1: part_o is float32 instead of the dtype of q */
   int32_t chunk_tiles;    /* scheduling: a column is dispatched in work items of at most this many
                              128-query tiles; 0 = the library's policy (moba_b200_chunk_tiles) */
+  int32_t win_begin;      /* query window: the transpose lists, and the partial buffers hold, only the */
+  int32_t win_rows;       /* query rows [win_begin, win_begin + win_rows) of every batch row; 0 = all rows.
+                             part_o, part_lse and dq_part are then [B, Hq, win_rows, slots(, D)]. Padded
+                             batches only. */
 } moba_b200_problem;
 
 typedef struct moba_b200_index {

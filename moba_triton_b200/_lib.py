@@ -36,7 +36,7 @@ class Problem(Structure):
     _fields_ = [(n, c_int32) for n in (
         "dtype", "batch", "tokens", "n_seq", "max_seqlen", "q_heads", "kv_heads", "head_dim",
         "block_size", "top_k", "slots", "take", "always_current", "num_blocks", "causal",
-        "packed", "path", "part_f32", "chunk_tiles")]
+        "packed", "path", "part_f32", "chunk_tiles", "win_begin", "win_rows")]
 
 
 class Index(Structure):
@@ -195,7 +195,9 @@ def set_kernel_path(path: int) -> int:
 
 def make_problem(q_shape, kv_heads: int, dtype: torch.dtype, cfg, cu_seqlens=None,
                  max_seqlen=None, causal: bool = True, part_f32: bool = False,
-                 chunk_tiles=None) -> Problem:
+                 chunk_tiles=None, window=None) -> Problem:
+    """The problem record of a call. `window` = (first query row, rows) restricts the call to
+    those query rows of every batch row (see `moba_b200_problem.win_begin`)."""
     b, s, hq, d = q_shape
     packed = cu_seqlens is not None
     n_seq = cu_seqlens.numel() - 1 if packed else b
@@ -207,4 +209,5 @@ def make_problem(q_shape, kv_heads: int, dtype: torch.dtype, cfg, cu_seqlens=Non
         slots=cfg.slots_per_query, take=cfg.past_blocks_selected(nb),
         always_current=int(cfg.always_select_current), num_blocks=nb, causal=int(causal),
         packed=int(packed), path=_force_path[0], part_f32=int(part_f32),
-        chunk_tiles=_chunk_tiles[0] if chunk_tiles is None else int(chunk_tiles))
+        chunk_tiles=_chunk_tiles[0] if chunk_tiles is None else int(chunk_tiles),
+        win_begin=0 if window is None else int(window[0]), win_rows=0 if window is None else int(window[1]))

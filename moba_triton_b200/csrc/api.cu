@@ -82,6 +82,12 @@ static int check_problem(const moba_b200_problem* p) {
     return MOBA_B200_EINVAL;
   }
   if (p->chunk_tiles < 0) { set_error("chunk_tiles must not be negative"); return MOBA_B200_EINVAL; }
+  if (p->win_begin < 0 || p->win_rows < 0 || (p->win_rows == 0 && p->win_begin != 0) ||
+      (long long)p->win_begin + p->win_rows > p->tokens) {
+    set_error("query window [%d, %d + %d) does not lie inside the %d rows", p->win_begin, p->win_begin, p->win_rows, p->tokens);
+    return MOBA_B200_EINVAL;
+  }
+  if (p->win_rows > 0 && p->packed) { set_error("a query window needs a padded batch, not a packed one"); return MOBA_B200_EUNSUPPORTED; }
   if ((long long)(p->q_heads / p->kv_heads) * p->max_seqlen * p->slots > 0x7fffffffLL) {
     set_error("a (sequence, kv head) column list would exceed 2^31 entries"); return MOBA_B200_EUNSUPPORTED;
   }

@@ -20,7 +20,7 @@ __global__ void fill_kernel(float* __restrict__ dst, size_t n, float value) {
 
 int launch_fill_lse(const moba_b200_problem& p, float* part_lse, cudaStream_t st) {
   KernelTimer timer__("fill_kernel", st);
-  const size_t n = (size_t)p.batch * p.q_heads * p.tokens * p.slots;
+  const size_t n = (size_t)p.batch * p.q_heads * window_rows(p) * p.slots;
   const int blocks = (int)((n + 1023) / 1024 < 148 * 8 ? (n + 1023) / 1024 : 148 * 8);
   fill_kernel<<<blocks > 0 ? blocks : 1, 256, 0, st>>>(part_lse, n, -INFINITY);
   MOBA_LAUNCH_OK("fill_kernel");
@@ -158,7 +158,7 @@ fwd_portable_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* _
 #pragma unroll
       for (int r = 0; r < kFwdRows; ++r) {
         if (row[r] < 0) continue;
-        const size_t dst = (((b * p.q_heads + head[r]) * p.tokens + row[r]) * (size_t)p.slots + slot[r]);
+        const size_t dst = part_row(p, b, head[r], row[r]) * (size_t)p.slots + slot[r];
         part_o[dst * d + c] = Elem<TP>::from_f(o[r] / l[r]);
       }
     }
@@ -166,7 +166,7 @@ fwd_portable_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* _
 #pragma unroll
     for (int r = 0; r < kFwdRows; ++r) {
       if (lane == r && row[r] >= 0) {
-        const size_t dst = (((b * p.q_heads + head[r]) * p.tokens + row[r]) * (size_t)p.slots + slot[r]);
+        const size_t dst = part_row(p, b, head[r], row[r]) * (size_t)p.slots + slot[r];
         part_lse[dst] = m[r] + log2f(l[r]);
       }
     }
@@ -218,7 +218,7 @@ template <typename TP, typename TO>
 __global__ void __launch_bounds__(256)
 merge_kernel(const TP* __restrict__ part_o, const float* __restrict__ part_lse,
              TO* __restrict__ out, float* __restrict__ lse_out, size_t n_rows, int tokens,
-             int q_heads, int d, int slots) {
+             int q_heads, int d, int slots, int win_begin, int win_rows) {
   constexpr int EPV = 16 / sizeof(TP);
   const int tpr = d / EPV;                                   // threads per row
   const size_t gid = (size_t)blockIdx.x * 256 + threadIdx.x;
@@ -258,7 +258,7 @@ merge_kernel(const TP* __restrict__ part_o, const float* __restrict__ part_lse,
     }
   }
   const float inv = 1.f / wsum;                              // wsum == 0 -> NaN, as the reference
-  const size_t s = r % tokens, bh = r / tokens;
+  const size_t s = win_begin + r % win_rows, bh = r / win_rows;     // r walks the window's rows
   const size_t h = bh % q_heads, b = bh / q_heads;
   TO* dst = out + ((b * tokens + s) * q_heads + h) * (size_t)d + c * EPV;
   __align__(16) TO packed_out[EPV];
@@ -266,13 +266,13 @@ merge_kernel(const TP* __restrict__ part_o, const float* __restrict__ part_lse,
   for (int e = 0; e < EPV; ++e) packed_out[e] = Elem<TO>::from_f(wsum > 0.f ? acc[e] * inv : NAN);
   if (sizeof(TO) * EPV == 16) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(packed_out);
   else *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(packed_out);
-  if (lse_out != nullptr && c == 0) lse_out[r] = (wsum > 0.f) ? mg + log2f(wsum) : -INFINITY;
+  if (lse_out != nullptr && c == 0) lse_out[bh * tokens + s] = (wsum > 0.f) ? mg + log2f(wsum) : -INFINITY;
 }
 
 int launch_merge(const moba_b200_problem& p, const void* part_o, const float* part_lse,
                  void* out, float* lse, cudaStream_t st) {
   KernelTimer timer__("merge_kernel", st);
-  const size_t n_rows = (size_t)p.batch * p.q_heads * p.tokens;
+  const size_t n_rows = (size_t)p.batch * p.q_heads * window_rows(p);
   const bool pf32 = p.part_f32 || p.dtype == MOBA_B200_F32;
   const int epv = pf32 ? 4 : 8;
   const int tpr = p.head_dim / epv;
@@ -281,7 +281,8 @@ int launch_merge(const moba_b200_problem& p, const void* part_o, const float* pa
   if (blocks == 0) return MOBA_B200_OK;
 #define MOBA_MERGE(TP, TO)                                                                      \
   merge_kernel<TP, TO><<<blocks, 256, 0, st>>>((const TP*)part_o, part_lse, (TO*)out, lse,      \
-                                               n_rows, p.tokens, p.q_heads, p.head_dim, p.slots)
+                                               n_rows, p.tokens, p.q_heads, p.head_dim, p.slots,      \
+                                               p.win_begin, window_rows(p))
   if (p.dtype == MOBA_B200_F32) MOBA_MERGE(float, float);
   else if (p.dtype == MOBA_B200_BF16) { if (pf32) MOBA_MERGE(float, __nv_bfloat16); else MOBA_MERGE(__nv_bfloat16, __nv_bfloat16); }
   else { if (pf32) MOBA_MERGE(float, __half); else MOBA_MERGE(__half, __half); }

@@ -344,7 +344,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
 
       // ---- epilogue of the same tile: O sits in the first D columns of this buffer ----
       const float inv = 1.f / l;
-      const size_t dst_row = ((c.b * p.q_heads + head) * p.tokens + row) * (size_t)p.slots + slot;
+      const size_t dst_row = part_row(p, c.b, head, row) * (size_t)p.slots + slot;
       TP* dst = part_o + dst_row * D;
       // A wait that gave up leaves TMEM unspecified: the tile then stores nothing.
       const bool o_ok = mbar_wait(&bars->o_full[wg], u & 1, wc, 3) && s_ok;

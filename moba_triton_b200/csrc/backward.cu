@@ -195,7 +195,7 @@ bwd_portable_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* _
     }
     // ---- phase 3 ----
     if (live) {
-      T* dst = dq_part + (((b * p.q_heads + head) * p.tokens + row) * (size_t)p.slots + slot) * d;
+      T* dst = dq_part + (part_row(p, b, head, row) * (size_t)p.slots + slot) * d;
       for (int c = lane; c < d; c += 32) {
         float acc = 0.f;
         for (int j = 0; j < keys; ++j) acc = fmaf(Ss[warp * bs + j], Elem<T>::to_f(Ks[j * kstride + c]), acc);
@@ -254,7 +254,8 @@ int launch_bwd_portable(const moba_b200_problem& p, const void* q, const void* k
 template <typename T>
 __global__ void __launch_bounds__(256)
 dq_reduce_kernel(const T* __restrict__ dq_part, const float* __restrict__ part_lse,
-                 T* __restrict__ dq, size_t n_rows, int tokens, int q_heads, int d, int slots) {
+                 T* __restrict__ dq, size_t n_rows, int tokens, int q_heads, int d, int slots,
+                 int win_begin, int win_rows) {
   constexpr int EPV = 16 / sizeof(T);
   const int tpr = d / EPV;
   const size_t gid = (size_t)blockIdx.x * 256 + threadIdx.x;
@@ -284,7 +285,7 @@ dq_reduce_kernel(const T* __restrict__ dq_part, const float* __restrict__ part_l
       for (int e = 0; e < EPV; ++e) acc[e] += Elem<T>::to_f(vals[e]);
     }
   }
-  const size_t s = r % tokens, bh = r / tokens;
+  const size_t s = win_begin + r % win_rows, bh = r / win_rows;     // r walks the window's rows
   const size_t h = bh % q_heads, b = bh / q_heads;
   __align__(16) T packed_out[EPV];
 #pragma unroll
@@ -298,11 +299,12 @@ int launch_dq_reduce(const moba_b200_problem& p, const void* dq_part, const floa
   KernelTimer timer__("dq_reduce_kernel", st);
   const int epv = 16 / (int)dtype_size(p.dtype);
   const int tpr = p.head_dim / epv;
-  const size_t n_rows = (size_t)p.batch * p.q_heads * p.tokens;
+  const size_t n_rows = (size_t)p.batch * p.q_heads * window_rows(p);
   const unsigned blocks = (unsigned)((n_rows * tpr + 255) / 256);
   if (!blocks) return MOBA_B200_OK;
 #define MOBA_DQR(T) \
-  dq_reduce_kernel<T><<<blocks, 256, 0, st>>>((const T*)dq_part, part_lse, (T*)dq, n_rows, p.tokens, p.q_heads, p.head_dim, p.slots)
+  dq_reduce_kernel<T><<<blocks, 256, 0, st>>>((const T*)dq_part, part_lse, (T*)dq, n_rows, p.tokens, p.q_heads, p.head_dim, p.slots, \
+                                              p.win_begin, window_rows(p))
   if (p.dtype == MOBA_B200_F32) MOBA_DQR(float);
   else if (p.dtype == MOBA_B200_BF16) MOBA_DQR(__nv_bfloat16);
   else MOBA_DQR(__half);

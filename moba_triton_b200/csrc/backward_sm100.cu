@@ -220,7 +220,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         const int row = mt.x < 0 ? 0 : mt.x, head = mt.y >> 8, slot = mt.y & 0xff;
         const bool live = mt.x >= 0;
         const float lse_r = __int_as_float(mt.z), delta_r = __int_as_float(mt.w);
-        const size_t qrow = (c.b * p.q_heads + head) * p.tokens + row;
         int jmax = live ? c.keys - 1 : -1;             // dead rows contribute nothing
         if (p.causal && live && (row - c.bos) / kTile == c.blk) jmax = min(jmax, row - c.key0);
 
@@ -296,7 +295,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         tc_fence_before();
         mbar_arrive(&bars->dq_read);                     // S / dQ columns may be overwritten
         if (wq == 0) bars->out_ptr[r] = (live && dq_ok) ? reinterpret_cast<unsigned char*>(
-                                                   dq_part + ((qrow * p.slots) + slot) * (size_t)D) : nullptr;
+                                                   dq_part + (part_row(p, c.b, head, row) * p.slots + slot) * (size_t)D) : nullptr;
         PHASE_ADD(wc, 22, ph);                           // dQ read and staged
         asm volatile("bar.sync 2, %0;" ::"n"(kElemThreads) : "memory");
         {
@@ -565,42 +564,51 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
 #endif
 }
 
-// dK / dV of the columns that were cut into several work items. The CTAs walk the work
-// items; at the first item of a split column a CTA adds the column's float32 partials in
-// item order and stores the result. Few columns are split (often none), so a CTA mostly
-// reads 16 bytes per item and moves on.
+// dK / dV of the columns that were cut into several work items. A CTA looks at 256
+// consecutive work items of one (sequence, kv head) row, one per thread; for every first item
+// of a split column among them it adds the column's float32 partials in item order and
+// stores the result. Few columns are split (often none), so most CTAs only read their items.
 template <int D, typename T>
 __global__ void __launch_bounds__(256)
 dkv_reduce_kernel(const float* __restrict__ dkv_scratch, moba_b200_index ix, const int32_t* __restrict__ cu,
-                  T* __restrict__ dk, T* __restrict__ dv, moba_b200_problem p, int n_kv_rows, int n_items) {
-  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-  const int kv_row = item % n_kv_rows, j = item / n_kv_rows;
-  const int4 it = __ldg(reinterpret_cast<const int4*>(ix.work_items) + (size_t)kv_row * ix.items_per_row + j);
-  if (it.w < 0 || it.y != 0) continue;                   // not the first item of a split column
-  const int nnz = ix.col_nnz[(size_t)kv_row * p.num_blocks + it.x];
-  const int tiles = (nnz + kTile - 1) / kTile;
-  const int n_chunks = (tiles + ix.chunk_tiles - 1) / ix.chunk_tiles;
+                  T* __restrict__ dk, T* __restrict__ dv, moba_b200_problem p, int ctas_per_row) {
+  __shared__ int4 found[256];
+  __shared__ int n_found;
+  const int kv_row = blockIdx.x / ctas_per_row;
+  const int j = (blockIdx.x % ctas_per_row) * 256 + threadIdx.x;
+  if (threadIdx.x == 0) n_found = 0;
+  __syncthreads();
+  if (j < ix.items_per_row) {
+    const int4 it = __ldg(reinterpret_cast<const int4*>(ix.work_items) + (size_t)kv_row * ix.items_per_row + j);
+    if (it.w >= 0 && it.y == 0) found[atomicAdd(&n_found, 1)] = it;    // the first item of a split column
+  }
+  __syncthreads();
   const int seq = kv_row / p.kv_heads, kvh = kv_row % p.kv_heads;
   const SeqSpan sp = seq_span(cu, p.packed, seq, p.tokens);
   const size_t b = p.packed ? 0 : (size_t)seq;
-  const int key0 = sp.bos + it.x * kTile;
-  const int keys = min(kTile, sp.bos + sp.len - key0);
-  constexpr int V4 = D / 4;                              // float4 per row
-  for (int i = threadIdx.x; i < 2 * kTile * V4; i += 256) {
-    const int which = i / (kTile * V4), row = (i / V4) % kTile, c4 = i % V4;
-    if (row >= keys) continue;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int c = 0; c < n_chunks; ++c) {
-      const float4 x = __ldcs(reinterpret_cast<const float4*>(
-          dkv_scratch + (((size_t)(it.w + c) * 2 + which) * kTile + row) * D) + c4);
-      acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+  for (int f = 0; f < n_found; ++f) {
+    const int4 it = found[f];
+    const int nnz = ix.col_nnz[(size_t)kv_row * p.num_blocks + it.x];
+    const int tiles = (nnz + kTile - 1) / kTile;
+    const int n_chunks = (tiles + ix.chunk_tiles - 1) / ix.chunk_tiles;
+    const int key0 = sp.bos + it.x * kTile;
+    const int keys = min(kTile, sp.bos + sp.len - key0);
+    constexpr int V4 = D / 4;                              // float4 per row
+    for (int i = threadIdx.x; i < 2 * kTile * V4; i += 256) {
+      const int which = i / (kTile * V4), row = (i / V4) % kTile, c4 = i % V4;
+      if (row >= keys) continue;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int c = 0; c < n_chunks; ++c) {
+        const float4 x = __ldcs(reinterpret_cast<const float4*>(
+            dkv_scratch + (((size_t)(it.w + c) * 2 + which) * kTile + row) * D) + c4);
+        acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+      }
+      T* dst = (which == 0 ? dv : dk) + ((b * p.tokens + key0 + row) * p.kv_heads + kvh) * (size_t)D + c4 * 4;
+      uint2 w;
+      w.x = pack2<T>(acc.x, acc.y);
+      w.y = pack2<T>(acc.z, acc.w);
+      *reinterpret_cast<uint2*>(dst) = w;
     }
-    T* dst = (which == 0 ? dv : dk) + ((b * p.tokens + key0 + row) * p.kv_heads + kvh) * (size_t)D + c4 * 4;
-    uint2 w;
-    w.x = pack2<T>(acc.x, acc.y);
-    w.y = pack2<T>(acc.z, acc.w);
-    *reinterpret_cast<uint2*>(dst) = w;
-  }
   }
 }
 
@@ -622,8 +630,9 @@ int launch_one(const moba_b200_problem& p, const CUtensorMap& km, const CUtensor
     MOBA_LAUNCH_OK("bwd_sm100_kernel");
   }
   KernelTimer timer__("dkv_reduce_kernel", st);
-  dkv_reduce_kernel<D, T><<<n_items < 4 * sms ? n_items : 4 * sms, 256, 0, st>>>(dkv_scratch, ix, cu, (T*)dk, (T*)dv, p,
-                                                                                 p.n_seq * p.kv_heads, n_items);
+  const int ctas_per_row = (ix.items_per_row + 255) / 256;
+  dkv_reduce_kernel<D, T><<<ctas_per_row * p.n_seq * p.kv_heads, 256, 0, st>>>(dkv_scratch, ix, cu, (T*)dk, (T*)dv, p,
+                                                                               ctas_per_row);
   MOBA_LAUNCH_OK("dkv_reduce_kernel");
   return MOBA_B200_OK;
 }

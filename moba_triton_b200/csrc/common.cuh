@@ -90,6 +90,16 @@ __device__ __forceinline__ SeqSpan seq_span(const int32_t* cu, int packed, int s
   return s;
 }
 
+// ---- query window: rows of the partial buffers ----
+// A call may cover only the query rows [win_begin, win_begin + win_rows) of every batch row
+// (host-side chunking along the query axis: the partial buffers, slots times the size of the
+// output, then exist for one window at a time). Row (b, head, row) of part_o / part_lse /
+// dq_part:
+__host__ __device__ inline int window_rows(const moba_b200_problem& p) { return p.win_rows > 0 ? p.win_rows : p.tokens; }
+__device__ __forceinline__ size_t part_row(const moba_b200_problem& p, size_t b, int head, int row) {
+  return (b * p.q_heads + head) * (size_t)window_rows(p) + (size_t)(row - p.win_begin);
+}
+
 // ---- launch table of the tensor-core kernels: one tile plan per head_dim ----
 // The kernels take their compile-time constants from this table, and moba_b200_launch_plan
 // reports it, so there is one place that says what runs. Shared memory decides the entries:
@@ -117,7 +127,7 @@ constexpr int kSchedSplit = 4;               // a column above total / (kSchedSp
 constexpr int kMinChunkTiles = 8;
 
 static inline long long sched_pairs_bound(const moba_b200_problem& p) {
-  return (long long)p.batch * p.tokens * p.q_heads * p.slots;     // every (query head, slot) pair
+  return (long long)p.batch * (p.win_rows > 0 ? p.win_rows : p.tokens) * p.q_heads * p.slots;   // every (query head, slot) pair
 }
 static inline int sched_chunk_tiles(const moba_b200_problem& p) {
   if (p.chunk_tiles > 0) return p.chunk_tiles;

@@ -67,8 +67,10 @@ count_kernel(const int32_t* __restrict__ block_idx, const int32_t* __restrict__ 
   for (int i = threadIdx.x; i < nb_lim; i += 256) hist[i] = 0;
   __syncthreads();
   const int32_t* src = block_idx + block_idx_row(p, seq, hq, sp.bos, row0);
-  const int n = rows * p.slots;
-  for (int e = threadIdx.x; e < n; e += 256) {
+  // only the rows inside the query window are listed (all of them without a window)
+  const int w_lo = max(0, p.win_begin - row0), w_hi = min(rows, (p.win_rows > 0 ? p.win_begin + p.win_rows : sp.len) - row0);
+  const int n = max(w_lo, w_hi) * p.slots;
+  for (int e = w_lo * p.slots + threadIdx.x; e < n; e += 256) {
     const int blk = src[e];
     if (blk >= 0 && blk < nb_lim) atomicAdd(&hist[blk], 1);
   }
@@ -292,8 +294,11 @@ scatter_kernel(const int32_t* __restrict__ block_idx, const int32_t* __restrict_
   const int32_t* pre = tile_prefix + (kv_row * p.num_blocks) * (group * C) + g * C + chunk;
   const int32_t* off = col_offsets + kv_row * (p.num_blocks + 1);
   // this warp's run of rows
-  const int run = (rows + W - 1) / W;
-  const int r_lo = min(rows, warp * run), r_hi = min(rows, r_lo + run);
+  // the chunk's rows inside the query window (all of them without a window), cut into W runs
+  const int w_lo = max(0, p.win_begin - row0);
+  const int w_hi = max(w_lo, min(rows, (p.win_rows > 0 ? p.win_begin + p.win_rows : sp.len) - row0));
+  const int run = (w_hi - w_lo + W - 1) / W;
+  const int r_lo = min(w_hi, w_lo + warp * run), r_hi = min(w_hi, r_lo + run);
   const int32_t* src = block_idx + block_idx_row(p, seq, hq, sp.bos, row0 + r_lo);
   const int n = (r_hi - r_lo) * p.slots;
   int* cursor = cursor_all + warp * nb_lim;
@@ -416,7 +421,7 @@ int launch_transpose(const moba_b200_problem& p, const int32_t* block_idx, const
     return MOBA_B200_EUNSUPPORTED;
   }
   const int group = p.q_heads / p.kv_heads;
-  const long long capacity = (long long)group * p.max_seqlen * p.slots;
+  const long long capacity = (long long)group * (p.win_rows > 0 ? p.win_rows : p.max_seqlen) * p.slots;
   if (hist_bytes > 48 * 1024) {
     MOBA_CUDA_OK(cudaFuncSetAttribute(count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hist_bytes));
     MOBA_CUDA_OK(cudaFuncSetAttribute(offsets_order_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hist_bytes));

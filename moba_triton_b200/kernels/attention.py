@@ -7,8 +7,9 @@ import torch
 from moba_triton_b200 import _lib
 from moba_triton_b200.config import MoBAConfig
 from moba_triton_b200.kernels.moba_bwd import moba_backward
-from moba_triton_b200.kernels.moba_fwd import _validate, attend_partials, merge_partials
-from moba_triton_b200.kernels.routing import CSCIndex, build_csc_fused
+from moba_triton_b200.kernels.moba_fwd import (_validate, attend_partials, forward_in_query_chunks,
+                                               merge_partials, query_windows)
+from moba_triton_b200.kernels.routing import CSCIndex, build_csc_from_indices, build_csc_fused
 
 
 class MoBAAttentionFunction(torch.autograd.Function):
@@ -38,6 +39,42 @@ class MoBAAttentionFunction(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None, None
 
 
+class MoBAQueryChunkedFunction(torch.autograd.Function):
+    """The op run a window of query rows at a time, forward and backward: the partial
+    outputs and dQ partials (slots times the size of the output) exist for one window only.
+    Saves the gate's block ids instead of an index; the backward rebuilds each window's
+    index from them. O and dQ are the bits of the whole call; dK/dV are summed over the
+    windows in float32 and rounded once."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, cfg, causal, query_chunk):
+        _validate(q, k, v, cfg, None, None)
+        _lib.require_cuda(q, k, v)
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        out, lse, block_idx = forward_in_query_chunks(q, k, v, cfg, query_chunk, causal, return_lse=True)
+        ctx.save_for_backward(q, k, v, out, lse, block_idx)
+        ctx.cfg, ctx.causal, ctx.query_chunk = cfg, causal, query_chunk
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse, block_idx = ctx.saved_tensors
+        cfg = ctx.cfg
+        nb = cfg.num_blocks(q.shape[1])
+        dq = torch.empty_like(q)
+        dk32 = torch.zeros(k.shape, device=k.device, dtype=torch.float32)
+        dv32 = torch.zeros(v.shape, device=v.device, dtype=torch.float32)
+        minus_inf = torch.full((), float("-inf"), device=q.device)
+        for window in query_windows(q.shape[1], ctx.query_chunk):
+            index = build_csc_from_indices(block_idx, nb, cfg, num_kv_heads=k.shape[2], window=window)
+            # which slots of the window's rows were written: those that name a block
+            marker = torch.where(block_idx[:, :, window[0]:window[0] + window[1]] >= 0, 0.0, minus_inf).contiguous()
+            _, dk_w, dv_w = moba_backward(dout, q, k, v, out, lse, marker, cfg, index, causal=ctx.causal, dq=dq)
+            dk32 += dk_w
+            dv32 += dv_w
+        return dq, dk32.to(k.dtype), dv32.to(v.dtype), None, None, None
+
+
 def _kv_head_passes(q, k, v, kv_heads_per_pass: int):
     """Slices of (q, k, v) that hold whole groups of query heads with their KV heads."""
     hkv = k.shape[2]
@@ -51,7 +88,8 @@ def moba_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cfg: MoBAC
                    index: Optional[CSCIndex] = None, causal: bool = True,
                    cu_seqlens: Optional[torch.Tensor] = None,
                    max_seqlen: Optional[int] = None,
-                   kv_heads_per_pass: Optional[int] = None) -> torch.Tensor:
+                   kv_heads_per_pass: Optional[int] = None,
+                   query_chunk: Optional[int] = None) -> torch.Tensor:
     """MoBA attention with gradient support.
 
     q [B,S,Hq,D]; k, v [B,S,Hkv,D] with Hkv dividing Hq (grouped-query heads map
@@ -66,7 +104,16 @@ def moba_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cfg: MoBAC
     heads are independent, so the result is the same bit for bit, while the
     per-(query, slot) partial outputs and dQ partials, which are `slots` times the
     size of the output, exist for one pass only: at q [1,524288,32,128] with 8 KV
-    heads that is 4.3 GB per pass instead of 34 GB."""
+    heads that is 4.3 GB per pass instead of 34 GB.
+
+    `query_chunk` (the chunking the reference describes there) runs `query_chunk` query
+    rows at a time instead, which also bounds the buffers when a GPU holds a single KV
+    head. Padded batches only. O and dQ come out bit for bit as from the whole call; dK and
+    dV are float32 sums over the windows, rounded once."""
+    if query_chunk is not None:
+        if index is not None or kv_heads_per_pass is not None or cu_seqlens is not None:
+            raise ValueError("query_chunk cannot be combined with index, kv_heads_per_pass or a packed batch")
+        return MoBAQueryChunkedFunction.apply(q, k, v, cfg, causal, query_chunk)
     if kv_heads_per_pass is not None:
         if index is not None:
             raise ValueError("kv_heads_per_pass cannot be combined with index (an index spans every head)")

@@ -15,7 +15,9 @@ from moba_triton_b200 import _lib
 from moba_triton_b200.config import MoBAConfig
 from moba_triton_b200.device import MIN_BLOCK_SIZE, check_gathered_head_dim
 from moba_triton_b200.gqa import head_group_size
-from moba_triton_b200.kernels.routing import CSCIndex, build_csc_fused
+from moba_triton_b200.kernels.gating import gate_select
+from moba_triton_b200.kernels.pooling import pool_blocks
+from moba_triton_b200.kernels.routing import CSCIndex, build_csc_from_indices, build_csc_fused
 from moba_triton_b200.varlen import validate_cu_seqlens
 
 
@@ -54,7 +56,8 @@ def _problem(q, k, cfg, index: CSCIndex, causal=True, part_f32=False):
     the index's work items were cut with."""
     return _lib.make_problem(tuple(q.shape), k.shape[2], q.dtype, cfg, index.cu_seqlens,
                              index.max_seqlen, causal=causal, part_f32=part_f32,
-                             chunk_tiles=index.chunk_tiles if index.work_items is not None else None)
+                             chunk_tiles=index.chunk_tiles if index.work_items is not None else None,
+                             window=index.window)
 
 
 def _check_index(q, k, cfg, index: CSCIndex) -> None:
@@ -88,7 +91,8 @@ def attend_partials(q, k, v, cfg: MoBAConfig, index: CSCIndex, causal: bool = Tr
     if partials_dtype not in (q.dtype, torch.float32):
         raise ValueError(f"partials_dtype must be {q.dtype} or float32, got {partials_dtype}")
     if partials is None:
-        partials = empty_partials(q.shape, index.max_slots, q.device, partials_dtype)
+        rows = q.shape[1] if index.window is None else index.window[1]
+        partials = empty_partials((q.shape[0], rows, q.shape[2], q.shape[3]), index.max_slots, q.device, partials_dtype)
     part_lse, part_o = partials
     prob = _problem(q, k, cfg, index, causal, part_o.dtype == torch.float32 and q.dtype != torch.float32)
     ix = index.c_struct()
@@ -97,20 +101,30 @@ def attend_partials(q, k, v, cfg: MoBAConfig, index: CSCIndex, causal: bool = Tr
     return part_lse, part_o
 
 
-def merge_partials(part_lse, part_o, out_dtype: torch.dtype, return_lse: bool = False):
+def merge_partials(part_lse, part_o, out_dtype: torch.dtype, return_lse: bool = False,
+                   out=None, lse=None, window=None):
     """LSE merge of (part_lse [B,H,S,K], part_o [B,H,S,K,D]) -> O [B,S,H,D]
-    (and lse [B,H,S], log2 units)."""
+    (and lse [B,H,S], log2 units). With `window` = (first row, rows) the partials hold
+    that query window only and rows [first, first + rows) of the given `out` (and `lse`)
+    are written."""
     _lib.require_cuda(part_lse, part_o)
     b, h, s, slots = part_lse.shape
     d = part_o.shape[-1]
     if tuple(part_o.shape) != (b, h, s, slots, d):
         raise ValueError(f"shape mismatch: part_o {tuple(part_o.shape)} against {(b, h, s, slots, d)}")
     part_lse, part_o = part_lse.contiguous(), part_o.contiguous()
-    out = torch.empty((b, s, h, d), device=part_o.device, dtype=out_dtype)
-    lse = torch.empty((b, h, s), device=part_o.device, dtype=torch.float32) if return_lse else None
+    if window is not None:
+        if out is None or s != window[1]:
+            raise ValueError("a windowed merge writes into `out`, and the partials hold window[1] rows")
+        s = out.shape[1]
+    if out is None:
+        out = torch.empty((b, s, h, d), device=part_o.device, dtype=out_dtype)
+    if lse is None and return_lse:
+        lse = torch.empty((b, h, s), device=part_o.device, dtype=torch.float32)
     cfg = MoBAConfig(block_size=16, top_k=slots, always_select_current=False)   # only `slots` matters here
     prob = _lib.make_problem((b, s, h, d), h, out_dtype, cfg,
-                             part_f32=part_o.dtype == torch.float32 and out_dtype != torch.float32)
+                             part_f32=part_o.dtype == torch.float32 and out_dtype != torch.float32,
+                             window=window)
     if part_o.dtype not in (out_dtype, torch.float32):
         raise ValueError(f"part_o must be {out_dtype} or float32, got {part_o.dtype}")
     _lib.call("moba_b200_merge", out.device, "combine_partials", prob, _lib.ptr(part_o), _lib.ptr(part_lse),
@@ -135,15 +149,58 @@ def combine_partials(part_m, part_l, part_acc, out_dtype: torch.dtype, block_m=N
     return merge_partials(lse, o.contiguous(), out_dtype, return_lse=return_lse)
 
 
+def query_windows(seq_len: int, query_chunk: int):
+    """(first row, rows) of the steps of a query-chunked call."""
+    if query_chunk < 1:
+        raise ValueError(f"query_chunk must be positive, got {query_chunk}")
+    return [(w0, min(query_chunk, seq_len - w0)) for w0 in range(0, seq_len, query_chunk)]
+
+
+def forward_in_query_chunks(q, k, v, cfg: MoBAConfig, query_chunk: int, causal: bool = True,
+                            partials_dtype: Optional[torch.dtype] = None, return_lse: bool = False):
+    """The forward run a window of `query_chunk` query rows at a time (padded batches): the
+    gate runs once, then every window gets its own index and reuses one set of partial
+    buffers of `query_chunk` rows. Every (query, block) pair is computed exactly as in the
+    whole call, so the output is the same bit for bit. Returns (out, lse or None, block_idx).
+    The reference planned this host-side chunking and never built it
+    (docs/deferred-decisions.md:152-220)."""
+    b, s, hq, d = q.shape
+    kbar = pool_blocks(k, cfg)
+    block_idx = gate_select(q, kbar, cfg)
+    out = torch.empty_like(q)
+    lse = torch.empty((b, hq, s), device=q.device, dtype=torch.float32) if return_lse else None
+    partials = None
+    for window in query_windows(s, query_chunk):
+        index = build_csc_from_indices(block_idx, kbar.shape[2], cfg, num_kv_heads=k.shape[2], window=window)
+        if partials is not None and partials[0].shape[2] != window[1]:
+            partials = None                                  # the last window may be shorter
+        part_lse, part_o = attend_partials(q, k, v, cfg, index, causal=causal, partials_dtype=partials_dtype,
+                                           partials=partials)
+        partials = (part_lse, part_o)
+        merge_partials(part_lse, part_o, q.dtype, return_lse=return_lse, out=out, lse=lse, window=window)
+    return out, lse, block_idx
+
+
 def moba_forward(q, k, v, cfg: MoBAConfig, index: Optional[CSCIndex] = None, causal: bool = True,
                  partials_dtype: Optional[torch.dtype] = None, cu_seqlens=None, max_seqlen=None,
-                 kv_heads_per_pass: Optional[int] = None):
+                 kv_heads_per_pass: Optional[int] = None, query_chunk: Optional[int] = None):
     """MoBA attention output [B,S,H,D] in the dtype of q (inference path; no
     log-sum-exp kept). Reference: moba_fwd.py:783-835.
 
     `kv_heads_per_pass` (not in the reference) runs that many KV heads at a time,
     each with its group of query heads, into one set of partial buffers that every
-    pass reuses: same result bit for bit, partial-output memory of one pass."""
+    pass reuses: same result bit for bit, partial-output memory of one pass.
+
+    `query_chunk` (not in the reference either) runs that many query rows at a time instead:
+    the partial buffers then hold `query_chunk` rows, whatever the number of heads. Padded
+    batches only; same result bit for bit."""
+    if query_chunk is not None:
+        if index is not None or kv_heads_per_pass is not None or cu_seqlens is not None:
+            raise ValueError("query_chunk cannot be combined with index, kv_heads_per_pass or a packed batch")
+        _validate(q, k, v, cfg, None, None)
+        _lib.require_cuda(q, k, v)
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        return forward_in_query_chunks(q, k, v, cfg, query_chunk, causal, partials_dtype)[0]
     if kv_heads_per_pass is not None:
         if index is not None:
             raise ValueError("kv_heads_per_pass cannot be combined with index (an index spans every head)")

@@ -44,6 +44,7 @@ class CSCIndex:
     max_seqlen: Optional[int] = None
     work_items: Optional[torch.Tensor] = None
     chunk_tiles: int = 0
+    window: Optional[tuple] = None      # (first query row, rows) when the index lists a query window only
 
     def c_struct(self) -> "_lib.Index":
         items = self.work_items
@@ -57,9 +58,11 @@ class CSCIndex:
 
 def build_csc_from_indices(block_idx: torch.Tensor, num_blocks: int, cfg: MoBAConfig,
                            num_kv_heads: Optional[int] = None, cu_seqlens=None,
-                           max_seqlen=None) -> CSCIndex:
+                           max_seqlen=None, window: Optional[tuple] = None) -> CSCIndex:
     """Transposes gate output [B,Hq,S,slots] (int32, -1 padded) into a CSCIndex,
-    entirely on the device and without a host synchronisation."""
+    entirely on the device and without a host synchronisation. `window` = (first row,
+    rows) lists only those query rows (padded batches): the index of one step of a
+    query-chunked call."""
     _lib.require_cuda(block_idx, cu_seqlens)
     b, hq, s, slots = block_idx.shape
     hkv = hq if num_kv_heads is None else num_kv_heads
@@ -72,12 +75,14 @@ def build_csc_from_indices(block_idx: torch.Tensor, num_blocks: int, cfg: MoBACo
     if slots != cfg.slots_per_query:
         raise ValueError(f"block_idx has {slots} slots per query, the configuration {cfg.slots_per_query}")
     # head_dim does not matter to the transpose; 64 keeps the problem record valid
-    prob = _lib.make_problem((b, s, hq, 64), hkv, torch.bfloat16, cfg, cu_seqlens, max_seqlen)
+    if window is not None and cu_seqlens is not None:
+        raise ValueError("a query window needs a padded batch, not a packed one")
+    prob = _lib.make_problem((b, s, hq, 64), hkv, torch.bfloat16, cfg, cu_seqlens, max_seqlen, window=window)
     if prob.num_blocks != num_blocks:
         raise ValueError(f"num_blocks {num_blocks} does not match the sequence length ({prob.num_blocks})")
     dev = block_idx.device
     block_idx = block_idx.contiguous()
-    cap = group * rows * slots
+    cap = group * (rows if window is None else window[1]) * slots
     i32 = dict(device=dev, dtype=torch.int32)
     col_nnz = torch.empty((n_seq, hkv, num_blocks), **i32)
     col_offsets = torch.empty((n_seq, hkv, num_blocks + 1), **i32)
@@ -98,7 +103,7 @@ def build_csc_from_indices(block_idx: torch.Tensor, num_blocks: int, cfg: MoBACo
     return CSCIndex(col_nnz, col_offsets, row_indices, head_indices, slot_of_pair, order,
                     num_blocks=num_blocks, max_slots=slots, num_query_heads=hq,
                     cu_seqlens=cu_seqlens, max_seqlen=max_seqlen,
-                    work_items=work_items, chunk_tiles=lib.moba_b200_chunk_tiles(prob))
+                    work_items=work_items, chunk_tiles=lib.moba_b200_chunk_tiles(prob), window=window)
 
 
 def build_csc_fused(q: torch.Tensor, k: torch.Tensor, cfg: MoBAConfig, cu_seqlens=None,

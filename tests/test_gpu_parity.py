@@ -402,3 +402,42 @@ def test_backend_adapter_runs_the_engine(device):
     assert torch.equal(out, moba.moba_forward(q, k, v, cfg))
     assert torch.equal(b.forward_grad(q, k, v, cfg), out)
     assert torch.equal(b.selection(q, k, cfg).cpu(), oracle_mask(q.cpu(), k.cpu(), cfg))
+
+
+def test_query_chunking_gives_the_whole_op(device, kernel_path):
+    """Running the op a window of query rows at a time (host-side chunking along the query
+    axis, which bounds the partial buffers whatever the number of heads): every (query,
+    block) pair is computed as in the whole call, so O and dQ are the same bits; dK/dV are
+    sums over the windows."""
+    cfg = moba.MoBAConfig(block_size=128, top_k=4, dtype=torch.bfloat16)
+    q, k, v, do = make_qkv((2, 1536, 4, 64), 2, dtype=torch.bfloat16, seed=29, with_do=True)
+    qd, kd, vd, dod = _dev(q, k, v, do, device=device)
+
+    def run(**kw):
+        qq, kk, vv = (t.clone().requires_grad_(True) for t in (qd, kd, vd))
+        out = moba.moba_attention(qq, kk, vv, cfg, **kw)
+        out.backward(dod)
+        return out.detach(), qq.grad, kk.grad, vv.grad
+
+    whole = run()
+    for chunk in (512, 640, 100, 4096):                     # aligned, ragged, below a block, above S
+        got = run(query_chunk=chunk)
+        assert torch.equal(got[0], whole[0]), f"output differs at query_chunk {chunk}"
+        assert torch.equal(got[1], whole[1]), f"dQ differs at query_chunk {chunk}"
+        assert torch.allclose(got[2].float(), whole[2].float(), rtol=2e-2, atol=2e-3)
+        assert torch.allclose(got[3].float(), whole[3].float(), rtol=2e-2, atol=2e-3)
+        assert torch.equal(moba.moba_forward(qd, kd, vd, cfg, query_chunk=chunk), whole[0])
+    with pytest.raises(ValueError, match="query_chunk"):
+        moba.moba_forward(qd, kd, vd, cfg, query_chunk=512, kv_heads_per_pass=1)
+    # the partial buffers of a chunked call hold one window
+    torch.cuda.synchronize()
+    torch.cuda.reset_peak_memory_stats(device)
+    base = torch.cuda.memory_allocated(device)
+    moba.moba_forward(qd, kd, vd, cfg, query_chunk=256)
+    torch.cuda.synchronize()
+    chunked_peak = torch.cuda.max_memory_allocated(device) - base
+    torch.cuda.reset_peak_memory_stats(device)
+    moba.moba_forward(qd, kd, vd, cfg)
+    torch.cuda.synchronize()
+    whole_peak = torch.cuda.max_memory_allocated(device) - base
+    assert chunked_peak < 0.6 * whole_peak, (chunked_peak, whole_peak)
