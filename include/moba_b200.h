@@ -2,10 +2,14 @@
  * moba_b200.h -- C ABI of the B200 (sm_100a) MoBA attention engine.
  *
  * Every entry point takes plain device pointers, a problem description and a
- * CUDA stream (passed as void*, a cudaStream_t). Nothing here allocates,
- * synchronises with the host or throws: the caller owns every buffer, work is
- * enqueued on the given stream, and the return value is 0 on success or a
- * negative MOBA_B200_E* code (text via moba_b200_last_error()).
+ * CUDA stream (passed as void*, a cudaStream_t). The compute entry points
+ * neither allocate device memory, synchronise with the host nor throw: the
+ * caller owns every buffer, work is enqueued on the given stream on the calling
+ * thread's current device, and the return value is 0 on success or a negative
+ * MOBA_B200_E* code (text via moba_b200_last_error()). Two service calls are
+ * the exception and say so: moba_b200_device_status waits for the stream, and
+ * while moba_b200_profile_enable(1) is in force every launch creates a pair of
+ * CUDA events (a measurement aid, off by default).
  *
  * Each declaration names the reference function it stands in for, by the path
  * inside the ZuricZ/moba-triton checkout.
@@ -77,6 +81,10 @@ typedef struct moba_b200_problem {
   int32_t part_f32;       /* 1: part_o is float32 instead of the dtype of q */
   int32_t chunk_tiles;    /* scheduling: a column is dispatched in work items of at most this many
                              128-query tiles; 0 = the library's policy (moba_b200_chunk_tiles) */
+  int32_t gate_window;    /* gate candidates (an extension, 0 = off = the reference's semantics): only the */
+  int32_t gate_sinks;     /* gate_window blocks before the query's own block, and the first gate_sinks
+                             blocks of the sequence, are scored and ranked; the gate then costs
+                             O(S * (window + sinks)) instead of O(S * num_blocks) */
   int32_t win_begin;      /* query window: the transpose lists, and the partial buffers hold, only the */
   int32_t win_rows;       /* query rows [win_begin, win_begin + win_rows) of every batch row; 0 = all rows.
                              part_o, part_lse and dq_part are then [B, Hq, win_rows, slots(, D)]. Padded

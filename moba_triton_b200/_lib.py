@@ -36,7 +36,7 @@ class Problem(Structure):
     _fields_ = [(n, c_int32) for n in (
         "dtype", "batch", "tokens", "n_seq", "max_seqlen", "q_heads", "kv_heads", "head_dim",
         "block_size", "top_k", "slots", "take", "always_current", "num_blocks", "causal",
-        "packed", "path", "part_f32", "chunk_tiles", "win_begin", "win_rows")]
+        "packed", "path", "part_f32", "chunk_tiles", "gate_window", "gate_sinks", "win_begin", "win_rows")]
 
 
 class Index(Structure):
@@ -210,4 +210,5 @@ def make_problem(q_shape, kv_heads: int, dtype: torch.dtype, cfg, cu_seqlens=Non
         always_current=int(cfg.always_select_current), num_blocks=nb, causal=int(causal),
         packed=int(packed), path=_force_path[0], part_f32=int(part_f32),
         chunk_tiles=_chunk_tiles[0] if chunk_tiles is None else int(chunk_tiles),
+        gate_window=int(getattr(cfg, "gate_window", None) or 0), gate_sinks=int(getattr(cfg, "gate_sinks", 0)),
         win_begin=0 if window is None else int(window[0]), win_rows=0 if window is None else int(window[1]))

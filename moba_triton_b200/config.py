@@ -8,6 +8,7 @@ and `pool_masked_only` is accepted and ignored, exactly as in the reference.
 """
 
 from dataclasses import dataclass
+from typing import Optional
 
 import torch
 
@@ -30,12 +31,23 @@ class MoBAConfig:
     top_k_includes_current: bool = True
     tie_break_low_index: bool = True
     pool_masked_only: bool = False
+    # Not in the reference. `gate_window` = W restricts the blocks a query may select to the W
+    # blocks before its own block plus the first `gate_sinks` blocks of its sequence; the gate
+    # then costs O(S * (W + sinks)) instead of O(S * num_blocks). None = every past block (the
+    # reference's semantics). It changes which blocks are chosen, so results differ from the
+    # reference's by design (the test suite's CPU restatement takes the same two parameters).
+    gate_window: Optional[int] = None
+    gate_sinks: int = 0
 
     def __post_init__(self) -> None:
         if self.block_size <= 0:
             raise ValueError(f"block_size must be positive, got {self.block_size}")
         if self.top_k <= 0:
             raise ValueError(f"top_k must be positive, got {self.top_k}")
+        if self.gate_window is not None and self.gate_window <= 0:
+            raise ValueError(f"gate_window must be positive or None, got {self.gate_window}")
+        if self.gate_sinks < 0 or (self.gate_sinks and self.gate_window is None):
+            raise ValueError("gate_sinks must not be negative and needs a gate_window")
 
     def past_blocks_selected(self, num_blocks: int) -> int:
         """Budget of strictly-past blocks per query, clamped to [0, num_blocks]

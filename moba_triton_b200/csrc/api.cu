@@ -82,6 +82,9 @@ static int check_problem(const moba_b200_problem* p) {
     return MOBA_B200_EINVAL;
   }
   if (p->chunk_tiles < 0) { set_error("chunk_tiles must not be negative"); return MOBA_B200_EINVAL; }
+  if (p->gate_window < 0 || p->gate_sinks < 0 || (p->gate_window == 0 && p->gate_sinks != 0)) {
+    set_error("gate_window / gate_sinks must not be negative, and sinks need a window"); return MOBA_B200_EINVAL;
+  }
   if (p->win_begin < 0 || p->win_rows < 0 || (p->win_rows == 0 && p->win_begin != 0) ||
       (long long)p->win_begin + p->win_rows > p->tokens) {
     set_error("query window [%d, %d + %d) does not lie inside the %d rows", p->win_begin, p->win_begin, p->win_rows, p->tokens);

@@ -564,10 +564,13 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
 #endif
 }
 
-// dK / dV of the columns that were cut into several work items. A CTA looks at 256
-// consecutive work items of one (sequence, kv head) row, one per thread; for every first item
-// of a split column among them it adds the column's float32 partials in item order and
-// stores the result. Few columns are split (often none), so most CTAs only read their items.
+// dK / dV of the columns that were cut into several work items. CTA (x, y) looks at 256
+// consecutive work items of one (sequence, kv head) row, one per thread, and of the first
+// items of split columns it finds there takes every kReduceSlices-th, starting at y: it adds
+// the column's float32 partials in item order and stores the result. Split columns are the
+// heaviest ones and therefore neighbours in the dispatch order, hence the slicing; most CTAs
+// find nothing and leave.
+constexpr int kReduceSlices = 16;
 template <int D, typename T>
 __global__ void __launch_bounds__(256)
 dkv_reduce_kernel(const float* __restrict__ dkv_scratch, moba_b200_index ix, const int32_t* __restrict__ cu,
@@ -578,36 +581,58 @@ dkv_reduce_kernel(const float* __restrict__ dkv_scratch, moba_b200_index ix, con
   const int j = (blockIdx.x % ctas_per_row) * 256 + threadIdx.x;
   if (threadIdx.x == 0) n_found = 0;
   __syncthreads();
-  if (j < ix.items_per_row) {
-    const int4 it = __ldg(reinterpret_cast<const int4*>(ix.work_items) + (size_t)kv_row * ix.items_per_row + j);
-    if (it.w >= 0 && it.y == 0) found[atomicAdd(&n_found, 1)] = it;    // the first item of a split column
-  }
+  int4 it = make_int4(0, 0, 0, -2);
+  if (j < ix.items_per_row)
+    it = __ldg(reinterpret_cast<const int4*>(ix.work_items) + (size_t)kv_row * ix.items_per_row + j);
+  const bool first = it.w >= 0 && it.y == 0;               // the first item of a split column
+  // position among the CTA's finds, in item order (so that the slices are the same on every run)
+  const unsigned ballot = __ballot_sync(0xffffffffu, first);
+  __shared__ int warp_finds[8];
+  if ((threadIdx.x & 31) == 0) warp_finds[threadIdx.x >> 5] = __popc(ballot);
+  __syncthreads();
+  int before = __popc(ballot & ((1u << (threadIdx.x & 31)) - 1u));
+  for (int w = 0; w < (int)(threadIdx.x >> 5); ++w) before += warp_finds[w];
+  if (first) found[before] = it;
+  if (threadIdx.x == 255) n_found = before + (first ? 1 : 0);
   __syncthreads();
   const int seq = kv_row / p.kv_heads, kvh = kv_row % p.kv_heads;
   const SeqSpan sp = seq_span(cu, p.packed, seq, p.tokens);
   const size_t b = p.packed ? 0 : (size_t)seq;
-  for (int f = 0; f < n_found; ++f) {
-    const int4 it = found[f];
-    const int nnz = ix.col_nnz[(size_t)kv_row * p.num_blocks + it.x];
+  for (int f = blockIdx.y; f < n_found; f += kReduceSlices) {
+    const int4 col = found[f];
+    const int nnz = ix.col_nnz[(size_t)kv_row * p.num_blocks + col.x];
     const int tiles = (nnz + kTile - 1) / kTile;
     const int n_chunks = (tiles + ix.chunk_tiles - 1) / ix.chunk_tiles;
-    const int key0 = sp.bos + it.x * kTile;
+    const int key0 = sp.bos + col.x * kTile;
     const int keys = min(kTile, sp.bos + sp.len - key0);
     constexpr int V4 = D / 4;                              // float4 per row
-    for (int i = threadIdx.x; i < 2 * kTile * V4; i += 256) {
-      const int which = i / (kTile * V4), row = (i / V4) % kTile, c4 = i % V4;
-      if (row >= keys) continue;
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    constexpr int kAhead = 4;                              // elements per thread in flight
+    for (int i0 = threadIdx.x; i0 < 2 * kTile * V4; i0 += 256 * kAhead) {
+      float4 acc[kAhead];
+#pragma unroll
+      for (int u = 0; u < kAhead; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int c = 0; c < n_chunks; ++c) {
-        const float4 x = __ldcs(reinterpret_cast<const float4*>(
-            dkv_scratch + (((size_t)(it.w + c) * 2 + which) * kTile + row) * D) + c4);
-        acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+#pragma unroll
+        for (int u = 0; u < kAhead; ++u) {
+          const int i = i0 + u * 256;
+          const int which = i / (kTile * V4), row = (i / V4) % kTile, c4 = i % V4;
+          if (row >= keys) continue;
+          const float4 x = __ldcs(reinterpret_cast<const float4*>(
+              dkv_scratch + (((size_t)(col.w + c) * 2 + which) * kTile + row) * D) + c4);
+          acc[u].x += x.x; acc[u].y += x.y; acc[u].z += x.z; acc[u].w += x.w;
+        }
       }
-      T* dst = (which == 0 ? dv : dk) + ((b * p.tokens + key0 + row) * p.kv_heads + kvh) * (size_t)D + c4 * 4;
-      uint2 w;
-      w.x = pack2<T>(acc.x, acc.y);
-      w.y = pack2<T>(acc.z, acc.w);
-      *reinterpret_cast<uint2*>(dst) = w;
+#pragma unroll
+      for (int u = 0; u < kAhead; ++u) {
+        const int i = i0 + u * 256;
+        const int which = i / (kTile * V4), row = (i / V4) % kTile, c4 = i % V4;
+        if (row >= keys) continue;
+        T* dst = (which == 0 ? dv : dk) + ((b * p.tokens + key0 + row) * p.kv_heads + kvh) * (size_t)D + c4 * 4;
+        uint2 w;
+        w.x = pack2<T>(acc[u].x, acc[u].y);
+        w.y = pack2<T>(acc[u].z, acc[u].w);
+        *reinterpret_cast<uint2*>(dst) = w;
+      }
     }
   }
 }
@@ -631,8 +656,8 @@ int launch_one(const moba_b200_problem& p, const CUtensorMap& km, const CUtensor
   }
   KernelTimer timer__("dkv_reduce_kernel", st);
   const int ctas_per_row = (ix.items_per_row + 255) / 256;
-  dkv_reduce_kernel<D, T><<<ctas_per_row * p.n_seq * p.kv_heads, 256, 0, st>>>(dkv_scratch, ix, cu, (T*)dk, (T*)dv, p,
-                                                                               ctas_per_row);
+  dkv_reduce_kernel<D, T><<<dim3(ctas_per_row * p.n_seq * p.kv_heads, kReduceSlices), 256, 0, st>>>(
+      dkv_scratch, ix, cu, (T*)dk, (T*)dv, p, ctas_per_row);
   MOBA_LAUNCH_OK("dkv_reduce_kernel");
   return MOBA_B200_OK;
 }

@@ -90,6 +90,14 @@ __device__ __forceinline__ SeqSpan seq_span(const int32_t* cu, int packed, int s
   return s;
 }
 
+// ---- gate candidates ----
+// Block `blk` is a candidate of a query whose own block is `own`: strictly past, and, when a
+// candidate window is set, among the first gate_sinks blocks or the last gate_window before
+// the own block.
+__host__ __device__ inline bool gate_candidate(const moba_b200_problem& p, int blk, int own) {
+  return blk < own && (p.gate_window <= 0 || blk < p.gate_sinks || blk >= own - p.gate_window);
+}
+
 // ---- query window: rows of the partial buffers ----
 // A call may cover only the query rows [win_begin, win_begin + win_rows) of every batch row
 // (host-side chunking along the query axis: the partial buffers, slots times the size of the

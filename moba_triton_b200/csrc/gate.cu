@@ -211,7 +211,7 @@ gate_portable_kernel(const T* __restrict__ q, const T* __restrict__ kbar,
       const int row = row0 + lrow;
       const int own = row / p.block_size;
       float s = Elem<T>::round_f((float)acc[r]);
-      if (!(blk < own && blk < n_cand && row < sp.len)) s = -INFINITY;
+      if (!(gate_candidate(p, blk, own) && blk < n_cand && row < sp.len)) s = -INFINITY;
       float* lv = lval + lrow * take;
       int* li = lidx + lrow * take;
       // offer the chunk's candidates in (score desc, id asc) order while they clear the bar

@@ -6,10 +6,10 @@
 // blocks a tile is exactly one block, so every row of a tile has the same
 // candidates: the blocks before the tile's own. Roles:
 //   loader (1 thread)  TMA: the unit's Q tile, then block-mean chunks of 128 blocks
-//   mma    (1 thread)  S = Q Kbar^T (M128 N128 K=D) into one of two TMEM buffers, every
-//                      chunk of the unit once, then every chunk again
+//   mma    (1 thread)  S = Q Kbar^T (M128 N128 K=D) into one of two TMEM buffers: the first
+//                      two chunks of the unit (bounding pass), then every chunk (ranking pass)
 //   select (2 x 4 warps; warpgroup w takes columns [64 w, 64 w + 64) of every chunk)
-//          tcgen05.ld, one row per thread. The chunks of a unit are scored twice.
+//          tcgen05.ld, one row per thread. The first two chunks of a unit are scored twice.
 //          The first pass only keeps, per row, the maxima of eight interleaved subsets
 //          of the scores (one max per score): the L-th largest of them is a score that
 //          at least L candidates reach, so nothing below it can be selected. The second
@@ -21,8 +21,8 @@
 //          in ascending block order, so an equal score never wins). A key is the score
 //          rounded to the input dtype and made monotone in the high half and
 //          0xFFFF - block id in the low half, so "score descending, ties to the lower
-//          id" is plain integer order. Scoring twice costs tensor-core time the gate has
-//          to spare; ranking every score once would cost issue slots it has not.
+//          id" is plain integer order. Scoring two chunks twice costs tensor-core time the
+//          gate has to spare; ranking every score would cost issue slots it has not.
 // At the end of a unit the two warpgroups' lists are merged and each thread emits
 // its ids plus the own block, ascending, -1 padded.
 //
@@ -128,7 +128,18 @@ __device__ __forceinline__ int unit_of(int round) {
 
 struct Unit {
   int tile, seq, hq, row0, n_chunks, bos, len;
+  int n_lo, c_hi0;          // chunks [0, n_lo) and [c_hi0, ...) of the Kbar row are visited
+  int n_first;              // chunks the bounding pass scores before the ranking pass scores all
+  // chunk of the Kbar row that step `s` of a pass scores
+  __device__ __forceinline__ int chunk_of(int s) const { return s < n_lo ? s : c_hi0 + (s - n_lo); }
+  // a unit takes n_first + n_chunks steps: the bounding pass, then the ranking pass
+  __device__ __forceinline__ int steps() const { return n_first + n_chunks; }
+  __device__ __forceinline__ int chunk_of_step(int step) const { return chunk_of(step < n_first ? step : step - n_first); }
 };
+// The bounding pass looks at the first two chunks only: 256 candidates give a bar that about
+// one score in ten of a later chunk passes until the first flush raises it, and scoring a long
+// row of block means twice would cost more tensor-core time than the tighter bar saves.
+constexpr int kBoundChunks = 2;
 __device__ __forceinline__ bool load_unit(Unit& u, int idx, const moba_b200_problem& p, const int32_t* cu,
                                           int n_tiles) {
   const int ny = p.n_seq * p.q_heads;
@@ -138,7 +149,18 @@ __device__ __forceinline__ bool load_unit(Unit& u, int idx, const moba_b200_prob
   const SeqSpan sp = seq_span(cu, p.packed, u.seq, p.tokens);
   u.bos = sp.bos; u.len = sp.len;
   u.row0 = u.tile * kTile;
-  u.n_chunks = (p.take > 0) ? (u.tile + kTile - 1) / kTile : 0;   // candidates: blocks [0, tile)
+  // Candidates are blocks [0, tile); with a candidate window only [0, sinks) and
+  // [tile - window, tile), so only the chunks that hold some of those are scored.
+  const int total = (p.take > 0) ? (u.tile + kTile - 1) / kTile : 0;
+  if (p.gate_window <= 0) {
+    u.n_lo = total; u.c_hi0 = total;
+  } else {
+    const int recent0 = max(0, u.tile - p.gate_window);         // first block of the recent window
+    u.n_lo = min(total, (min(p.gate_sinks, recent0) + kTile - 1) / kTile);
+    u.c_hi0 = max(u.n_lo, recent0 / kTile);
+  }
+  u.n_chunks = u.n_lo + (total - u.c_hi0);
+  u.n_first = min(u.n_chunks, kBoundChunks);
   return u.row0 < sp.len;
 }
 
@@ -232,11 +254,11 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         PHASE_ADD(wc, 4, fl);                                   // flushes (also counted in their phase)
       };
       PHASE_ADD(wc, 1, ph);                                     // unit set-up
-      for (int step = 0; step < 2 * u.n_chunks; ++step) {
+      for (int step = 0; step < u.steps(); ++step) {
         const uint32_t gidx = gc + (uint32_t)step, st = gidx & 1u;
-        const bool second = step >= u.n_chunks;
-        const int c = second ? step - u.n_chunks : step;
-        if (second && c == 0) {
+        const bool second = step >= u.n_first;
+        const int c = u.chunk_of_step(step);
+        if (step == u.n_first) {
           // The L-th largest of the eight subset maxima: at least L candidates reach it.
           float lo1 = INFINITY, lo2 = INFINITY;                 // smallest and second smallest
 #pragma unroll
@@ -249,8 +271,7 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         const bool s_ok = mbar_wait(&bars->s_full[st], (gidx >> 1) & 1u, wc, 9);
         tc_fence_after();
         PHASE_ADD(wc, 2, ph);                                   // s_full wait
-        const int c0 = c * kTile + wg * 64;                     // first column of this warpgroup's half
-        const int cmax = u.tile - c0;                           // its columns [0, cmax) are candidates
+        const int c0 = c * kTile + wg * 64;                     // first column (block) of this warpgroup's half
         const bool run = __all_sync(0xffffffffu, s_ok);         // a wait gave up: rank nothing unseen
         uint32_t v[32];
 #pragma unroll 1
@@ -258,11 +279,16 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
           tmem_ld32(tmem + lane_off + st * 128 + wg * 64 + h * 32, v);
           tmem_ld_wait();
           if (h == 1) { tc_fence_before(); mbar_arrive(&bars->s_free[st]); }   // the scores are in registers
-          if (!run || h * 32 >= cmax) continue;
-          if (cmax < h * 32 + 32) {
+          // which of these 32 blocks are candidates of the tile: all, none, or some
+          const int g0 = c0 + h * 32;
+          const bool none = g0 >= u.tile || (p.gate_window > 0 && g0 >= p.gate_sinks && g0 + 32 <= u.tile - p.gate_window);
+          if (!run || none) continue;
+          const bool all = g0 + 32 <= u.tile &&
+                           (p.gate_window <= 0 || g0 + 32 <= p.gate_sinks || g0 >= u.tile - p.gate_window);
+          if (!all) {
 #pragma unroll
             for (int k = 0; k < 32; ++k)
-              if (h * 32 + k >= cmax) v[k] = 0xff800000u;       // -inf: never a candidate
+              if (!gate_candidate(p, g0 + k, u.tile)) v[k] = 0xff800000u;   // -inf: never passes
           }
           if (!second) {
 #pragma unroll
@@ -291,7 +317,7 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         PHASE_ADD(wc, 3, ph);                                   // loads, maxima / tests and appends, flushes
       }
       flush();
-      gc += 2u * (uint32_t)u.n_chunks;
+      gc += (uint32_t)u.steps();
       // ---- merge the two warpgroups' lists (warpgroup 1 -> warpgroup 0's empty buffer) ----
       asm volatile("bar.sync 2, 256;" ::: "memory");            // warpgroup 0 has emptied its buffer
       if (wg == 1) {
@@ -345,7 +371,7 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         Unit u;
         if (!load_unit(u, ui, p, cu, n_tiles) || u.n_chunks == 0) continue;
         mbar_wait(&bars->q_full, nq & 1, wc);
-        for (int step = 0; step < 2 * u.n_chunks; ++step, ++gc) {
+        for (int step = 0; step < u.steps(); ++step, ++gc) {
           const uint32_t st = gc & 1, use = gc >> 1;
           const uint32_t aK = smem_u32(sKb) + st * Cfg::kOperand;
           mbar_wait(&bars->kb_full[st], use & 1, wc);
@@ -384,9 +410,9 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         mbar_expect_tx(&bars->q_full, Cfg::kOperand);
         for (int s = 0; s < Cfg::kSubs; ++s) tma_load_3d(sQ + s * kSub, &q_map, &bars->q_full, s * 64, u.hq, tok0);
         ++nq;
-        for (int step = 0; step < 2 * u.n_chunks; ++step, ++gc) {
+        for (int step = 0; step < u.steps(); ++step, ++gc) {
           const uint32_t st = gc & 1, use = gc >> 1;
-          const int c = step >= u.n_chunks ? step - u.n_chunks : step;
+          const int c = u.chunk_of_step(step);
           if (use >= 1) mbar_wait(&bars->kb_empty[st], (use - 1) & 1, wc);
           if (*wc.abort) break;
           mbar_expect_tx(&bars->kb_full[st], Cfg::kOperand);

@@ -122,12 +122,19 @@ def gate_scores(q_seq: torch.Tensor, kbar_seq: torch.Tensor) -> torch.Tensor:
 
 def select_blocks_seq(scores: torch.Tensor, block_size: int, top_k: int,
                       always_current: bool = True,
-                      includes_current: bool = True) -> torch.Tensor:
-    """scores [Hq, S, nb] -> bool mask [Hq, S, nb] (reference: naive.py:111-146)."""
+                      includes_current: bool = True,
+                      gate_window: Optional[int] = None, gate_sinks: int = 0) -> torch.Tensor:
+    """scores [Hq, S, nb] -> bool mask [Hq, S, nb] (reference: naive.py:111-146).
+
+    `gate_window` / `gate_sinks` are this engine's candidate restriction (no counterpart in
+    the reference): only the `gate_window` blocks before the own block and the first
+    `gate_sinks` blocks are ranked."""
     hq, s, nb = scores.shape
     own = torch.arange(s) // block_size
     blocks = torch.arange(nb)
     is_past = blocks.view(1, nb) < own.view(s, 1)
+    if gate_window is not None:
+        is_past &= (blocks.view(1, nb) < gate_sinks) | (blocks.view(1, nb) >= own.view(s, 1) - gate_window)
     masked = scores.to(torch.float64).masked_fill(~is_past.view(1, s, nb), float("-inf"))
     order = torch.argsort(masked, dim=-1, descending=True, stable=True)
     take = past_budget(top_k, nb, always_current, includes_current)
@@ -142,7 +149,7 @@ def select_blocks_seq(scores: torch.Tensor, block_size: int, top_k: int,
 def selection_mask(q: torch.Tensor, k: torch.Tensor, block_size: int, top_k: int,
                    cu_seqlens=None, max_seqlen: Optional[int] = None,
                    always_current: bool = True, includes_current: bool = True,
-                   return_scores: bool = False):
+                   return_scores: bool = False, gate_window: Optional[int] = None, gate_sinks: int = 0):
     """Bool [B|1, Hq, S|T, nb]; packed block ids are sequence-local and the last
     axis is sized by the longest sequence (reference: naive.py:149-189)."""
     kbar = pool_blocks(k, block_size, cu_seqlens, max_seqlen)
@@ -158,7 +165,7 @@ def selection_mask(q: torch.Tensor, k: torch.Tensor, block_size: int, top_k: int
         nb = num_blocks(hi - lo, block_size)
         sc = gate_scores(q[b, lo:hi], kbar[row, :, :nb])
         out[b, :, lo:hi, :nb] = select_blocks_seq(sc, block_size, top_k,
-                                                  always_current, includes_current)
+                                                  always_current, includes_current, gate_window, gate_sinks)
         if return_scores:
             sc_out[b, :, lo:hi, :nb] = sc.to(torch.float64)
     return (out, sc_out) if return_scores else out

@@ -18,7 +18,9 @@ import sys
 import numpy as np
 import torch
 
-REF = os.environ.get("MOBA_REFERENCE_SRC", "/root/reference/src")
+REF = os.environ.get("MOBA_REFERENCE_SRC")
+if not REF:
+    raise SystemExit("set MOBA_REFERENCE_SRC to the `src` directory of a ZuricZ/moba-triton checkout")
 sys.path.insert(0, REF)
 
 from moba.config import MoBAConfig                       # noqa: E402  (reference)

@@ -24,7 +24,7 @@ def oracle_mask(q, k, cfg, cu=None, max_seqlen=None, return_scores=False):
     return orc.selection_mask(q.cpu(), k.cpu(), cfg.block_size, cfg.top_k, cu_seqlens=cu,
                               max_seqlen=max_seqlen, always_current=cfg.always_select_current,
                               includes_current=cfg.top_k_includes_current,
-                              return_scores=return_scores)
+                              return_scores=return_scores, gate_window=cfg.gate_window, gate_sinks=cfg.gate_sinks)
 
 
 def near_tie_report(engine_mask, oracle_mask_, scores, mantissa_bits: int):

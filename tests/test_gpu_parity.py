@@ -441,3 +441,14 @@ def test_query_chunking_gives_the_whole_op(device, kernel_path):
     torch.cuda.synchronize()
     whole_peak = torch.cuda.max_memory_allocated(device) - base
     assert chunked_peak < 0.6 * whole_peak, (chunked_peak, whole_peak)
+
+
+def test_candidate_window_gate_on_both_kernel_families(device, kernel_path):
+    cfg = moba.MoBAConfig(32, 4, gate_window=5, gate_sinks=2)
+    q, k, _ = make_qkv((2, 1024, 2, 64), dtype=torch.bfloat16, seed=33)
+    idx = moba.gate_select(q.to(device), moba.pool_blocks(k.to(device), cfg), cfg).cpu()
+    want = orc.mask_to_block_idx(oracle_mask(q, k, cfg), cfg.slots_per_query)
+    assert torch.equal(idx, want)
+    wide = moba.MoBAConfig(32, 4, gate_window=64)
+    idx2 = moba.gate_select(q.to(device), moba.pool_blocks(k.to(device), wide), wide).cpu()
+    assert torch.equal(idx2, orc.mask_to_block_idx(oracle_mask(q, k, moba.MoBAConfig(32, 4)), 4))

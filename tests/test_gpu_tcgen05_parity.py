@@ -245,3 +245,36 @@ def test_split_columns_give_the_same_results(d, hq, hkv, cu, device, tiny_chunks
     assert torch.equal(got[0], whole[0]) and torch.equal(got[1], whole[1])
     assert torch.allclose(got[2].float(), whole[2].float(), rtol=2e-2, atol=2e-3)
     assert torch.allclose(got[3].float(), whole[3].float(), rtol=2e-2, atol=2e-3)
+
+
+# ---------------------------------------------------------------------------
+# the candidate-window gate (an extension: bounds the gate's cost; not the reference's semantics)
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("window,sinks", [(4, 0), (4, 2), (130, 1), (1, 0), (40, 150), (100000, 0)])
+def test_candidate_window_gate_selects_by_the_stated_rule(window, sinks, device):
+    """300 blocks, so the recent window and the sinks fall into different 128-block chunks
+    and the chunks between them are skipped. The selection is compared with the CPU
+    restatement of the same rule; a window wider than the sequence is the unrestricted gate."""
+    nb = 300
+    shape = (1, 128 * nb, 2, 64)
+    cfg = moba.MoBAConfig(128, 8, gate_window=window, gate_sinks=sinks)
+    assert_on_tensor_core_path(shape, 1, torch.bfloat16, cfg)
+    q, k, _ = make_qkv(shape, 1, dtype=torch.bfloat16, seed=61)
+    qd, kd = q.to(device), k.to(device)
+    idx = moba.gate_select(qd, moba.pool_blocks(kd, cfg), cfg).cpu()
+    mask = orc.block_idx_to_mask(idx, nb)
+    _check_selection(mask, q, k, cfg, torch.bfloat16)
+    own = (torch.arange(shape[1]) // 128).view(1, 1, -1, 1)
+    blocks = torch.arange(nb).view(1, 1, 1, -1)
+    allowed = (blocks == own) | ((blocks < own) & ((blocks < sinks) | (blocks >= own - window)))
+    assert not (mask & ~allowed).any(), "a block outside the candidate window was selected"
+    if window >= nb:
+        plain = moba.gate_select(qd, moba.pool_blocks(kd, cfg), moba.MoBAConfig(128, 8)).cpu()
+        assert torch.equal(idx, plain)
+
+
+def test_candidate_window_through_the_whole_op(device):
+    cfg = moba.MoBAConfig(128, 4, gate_window=3, gate_sinks=1)
+    _check_op((1, 2048, 4, 64), 2, torch.bfloat16, cfg, device, seed=63)
+    _check_op((1, 1841, 4, 128), 2, torch.bfloat16, cfg, device, cu=[0, 384, 513, 1513, 1641, 1841], seed=64)

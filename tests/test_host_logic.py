@@ -224,3 +224,44 @@ def test_launch_plan_is_a_table_lookup_on_the_problem_record():
         assert packed[key] == alone[key]
     with pytest.raises(ValueError):
         launch_plan((1, 64, 3, 64), 2, torch.bfloat16, cfg)
+
+
+def test_reference_arm_of_the_bench_prints_the_contract_line():
+    """`bench.py --impl reference` needs no GPU: it times the oracle on the host cores and
+    prints one JSON line whose `config` is the object our arm prints for the same workload."""
+    import json
+    import subprocess
+    import sys
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1",
+                          "--warmup", "0", "--workload", "small"], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["unit"] == "TFLOP/s" and line["higher_is_better"] is True
+    assert line["value"] > 0 and line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
+    assert line["e2e"] == {"value": line["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    import bench
+    wl = bench.describe("small", 0, 1)
+    assert line["config"] == bench.base_config(wl, 8192)
+    assert set(line["config"]) == {"workload", "tokens_all_gpus", "l2"}
+
+
+def test_candidate_window_rule_of_the_restatement_and_the_config():
+    from oracle import moba_oracle as orc
+    g = torch.Generator().manual_seed(1)
+    q = torch.randn(1, 512, 1, 64, generator=g)
+    k = torch.randn(1, 512, 1, 64, generator=g)
+    full = orc.selection_mask(q, k, 32, 4)
+    assert torch.equal(orc.selection_mask(q, k, 32, 4, gate_window=64), full)       # wider than the sequence
+    win = orc.selection_mask(q, k, 32, 4, gate_window=2, gate_sinks=1)[0, 0]        # [S, nb]
+    own = torch.arange(512) // 32
+    for s in (100, 300, 511):
+        chosen = set(win[s].nonzero().flatten().tolist())
+        allowed = {0, own[s].item() - 2, own[s].item() - 1, own[s].item()}
+        assert chosen <= allowed and own[s].item() in chosen and len(chosen) == min(4, len(allowed))
+    with pytest.raises(ValueError):
+        moba.MoBAConfig(32, 4, gate_window=0)
+    with pytest.raises(ValueError):
+        moba.MoBAConfig(32, 4, gate_sinks=2)
+    prob = _lib.make_problem((1, 512, 2, 64), 2, torch.bfloat16, moba.MoBAConfig(32, 4, gate_window=7, gate_sinks=3))
+    assert (prob.gate_window, prob.gate_sinks) == (7, 3)
+    assert _lib.make_problem((1, 512, 2, 64), 2, torch.bfloat16, moba.MoBAConfig(32, 4)).gate_window == 0
