@@ -162,12 +162,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->k_full, 1); mbar_init(&bars->v_full, 1);
-    mbar_init(&bars->k_fix, 32); mbar_init(&bars->v_fix, 32);
+    mbar_init(&bars->k_fix, 1); mbar_init(&bars->v_fix, 1);
     mbar_init(&bars->k_free, 1); mbar_init(&bars->v_free, 1);
     for (int i = 0; i < 4; ++i) {
-      mbar_init(&bars->q_full[i], 128); mbar_init(&bars->q_empty[i], 1);
-      mbar_init(&bars->s_full[i], 1); mbar_init(&bars->p_full[i], 128);
-      mbar_init(&bars->o_full[i], 1); mbar_init(&bars->so_free[i], 128);
+      mbar_init(&bars->q_full[i], 4); mbar_init(&bars->q_empty[i], 1);
+      mbar_init(&bars->s_full[i], 1); mbar_init(&bars->p_full[i], 4);
+      mbar_init(&bars->o_full[i], 1); mbar_init(&bars->so_free[i], 4);
       mbar_init(&bars->col_full[i], 1);
     }
     mbar_init(&bars->drain[0], 1); mbar_init(&bars->drain[1], 1);
@@ -266,7 +266,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         gather(cur, row, head);
         cp_async_wait<0>();
         fence_proxy_async();
-        mbar_arrive(&bars->q_full[wg]);
+        mbar_arrive_warp(&bars->q_full[wg]);
       }
       PHASE_ADD(wc, 10, ph);                           // late gather
       int jmax = c.keys - 1;
@@ -338,8 +338,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       if (nxt == 1) cp_async_wait<0>();                // the next tile's rows have landed
       fence_proxy_async();                             // P and those rows -> visible to the MMA
       tc_fence_before();
-      mbar_arrive(&bars->p_full[wg]);
-      if (nxt == 1) mbar_arrive(&bars->q_full[wg]);
+      mbar_arrive_warp(&bars->p_full[wg]);
+      if (nxt == 1) mbar_arrive_warp(&bars->q_full[wg]);
       PHASE_ADD(wc, 15, ph);                           // copies landed, fences, arrivals
 
       // ---- epilogue of the same tile: O sits in the first D columns of this buffer ----
@@ -375,7 +375,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         }
       }
       tc_fence_before();
-      mbar_arrive(&bars->so_free[wg]);               // the TMEM buffer may be overwritten
+      mbar_arrive_warp(&bars->so_free[wg]);               // the TMEM buffer may be overwritten
       PHASE_ADD(wc, 17, ph);                           // O read and staged
       if (live && o_ok) st_global_stream_f32(part_lse + dst_row, m2 + log2f(l));
       if (sizeof(TP) == 2) {
@@ -526,14 +526,14 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
           *reinterpret_cast<uint4*>(sK + s * kSub + rr * 128 + ch * 16) = make_uint4(0, 0, 0, 0);
         }
         fence_proxy_async();
-        mbar_arrive(&bars->k_fix);
+        mbar_arrive_warp(&bars->k_fix);
         mbar_wait(&bars->v_full, it_cnt & 1, wc, 8);
         for (int i = lane; i < dead * 8 * Cfg::kSubs; i += 32) {
           const int s = i / (dead * 8), rr = c.keys + (i % (dead * 8)) / 8, ch = i % 8;
           *reinterpret_cast<uint4*>(sV + s * kSub + rr * 128 + ch * 16) = make_uint4(0, 0, 0, 0);
         }
         fence_proxy_async();
-        mbar_arrive(&bars->v_fix);
+        mbar_arrive_warp(&bars->v_fix);
       }
       ++it_cnt;
     }

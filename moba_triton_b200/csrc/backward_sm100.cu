@@ -161,12 +161,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->k_full[i], 1); mbar_init(&bars->v_full[i], 1); mbar_init(&bars->kv_free[i], 1);
-      mbar_init(&bars->qd_full[i], 128); mbar_init(&bars->qd_empty[i], 1);
+      mbar_init(&bars->qd_full[i], 4); mbar_init(&bars->qd_empty[i], 1);
     }
-    mbar_init(&bars->k_fix, 128); mbar_init(&bars->v_fix, 128);
-    mbar_init(&bars->sp_full, 1); mbar_init(&bars->pds_full, kElemThreads);
-    mbar_init(&bars->dq_full, 1); mbar_init(&bars->dq_read, kElemThreads);
-    mbar_init(&bars->acc_full, 1); mbar_init(&bars->acc_read, kElemThreads); mbar_init(&bars->drain, 1);
+    mbar_init(&bars->k_fix, 4); mbar_init(&bars->v_fix, 4);
+    mbar_init(&bars->sp_full, 1); mbar_init(&bars->pds_full, kElemWarps);
+    mbar_init(&bars->dq_full, 1); mbar_init(&bars->dq_read, kElemWarps);
+    mbar_init(&bars->acc_full, 1); mbar_init(&bars->acc_read, kElemWarps); mbar_init(&bars->drain, 1);
     bars->abort = 0;
     fence_barrier_init();
   }
@@ -216,6 +216,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         PHASE_ADD(wc, 16, ph);                           // between tiles
         const bool sp_ok = mbar_wait(&bars->sp_full, t & 1, wc, 1);
         PHASE_ADD(wc, 17, ph);                           // sp_full wait
+        TRACE(error_word, t, 0);
         const int4 mt = sp_ok ? bars->meta[t % NST][r] : make_int4(-1, 0, 0, 0);
         const int row = mt.x < 0 ? 0 : mt.x, head = mt.y >> 8, slot = mt.y & 0xff;
         const bool live = mt.x >= 0;
@@ -263,15 +264,18 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
           if (all_open) p_ds(std::false_type{}); else p_ds(std::true_type{});
         }
         PHASE_ADD(wc, 19, ph);                           // P, dS: loads, arithmetic, stores
+        TRACE(error_word, t, 1);
         fence_proxy_async();
         tc_fence_before();
-        mbar_arrive(&bars->pds_full);
+        mbar_arrive_warp(&bars->pds_full);
         PHASE_ADD(wc, 20, ph);                           // fences, arrival
+        TRACE(error_word, t, 2);
 
         // ---- dQ rows of this tile: this quarter stores columns [wq D/4, (wq+1) D/4) ----
         const bool dq_ok = mbar_wait(&bars->dq_full, t & 1, wc, 2);
         tc_fence_after();
         PHASE_ADD(wc, 21, ph);                           // dq_full wait
+        TRACE(error_word, t, 3);
         // Stage the 16-bit dQ tile in shared memory (a tile of its own, or the P buffer once
         // dV has read it) so that eight or sixteen adjacent lanes write each row; one row per
         // thread straight to global memory would touch 32 lines per instruction.
@@ -293,11 +297,13 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
           }
         }
         tc_fence_before();
-        mbar_arrive(&bars->dq_read);                     // S / dQ columns may be overwritten
+        mbar_arrive_warp(&bars->dq_read);                     // S / dQ columns may be overwritten
         if (wq == 0) bars->out_ptr[r] = (live && dq_ok) ? reinterpret_cast<unsigned char*>(
                                                    dq_part + (part_row(p, c.b, head, row) * p.slots + slot) * (size_t)D) : nullptr;
         PHASE_ADD(wc, 22, ph);                           // dQ read and staged
+        TRACE(error_word, t, 4);
         asm volatile("bar.sync 2, %0;" ::"n"(kElemThreads) : "memory");
+        TRACE(error_word, t, 5);
         {
           constexpr int CPRO = D / 8;                    // 16-byte chunks per row
           constexpr int RPPO = kElemThreads / CPRO;      // rows per pass of the elementwise threads
@@ -313,6 +319,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         }
         asm volatile("bar.sync 2, %0;" ::"n"(kElemThreads) : "memory");   // the staging tile may be written again
         PHASE_ADD(wc, 23, ph);                           // barriers and dQ stores
+        TRACE(error_word, t, 6);
       }
       // ---- the column's dV (quarters 0, 1) and dK (quarters 2, 3): half of a key row per thread ----
       const bool acc_ok = mbar_wait(&bars->acc_full, it_cnt & 1, wc, 3);
@@ -348,7 +355,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         }
       }
       tc_fence_before();
-      mbar_arrive(&bars->acc_read);
+      mbar_arrive_warp(&bars->acc_read);
       ++it_cnt;
     }
   } else if (warp == kMmaWarp) {
@@ -377,6 +384,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
           const uint32_t st = t % NST, us = t / NST;
           const uint32_t aQ = smem_u32(sQ) + st * Cfg::kOperand, aG = smem_u32(sG) + st * Cfg::kOperand;
           mbar_wait(&bars->qd_full[st], us & 1, wc, 8);
+          TRACE(error_word, t, 0);
           // Where dQ shares the S columns and its staging the P tile, S of this tile waits for
           // the previous dQ to be read out. With columns and a staging tile of its own, S and
           // dP run while the elementwise warps write dQ out: they finished reading S and dP
@@ -394,8 +402,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
             if (leader) umma_f16(tmem + cDP, make_sdesc(aG + o, 16, 1024), make_sdesc(aV + o, 16, 1024), id_s, ks > 0);
           }
           if (leader) umma_commit(&bars->sp_full);
+          TRACE(error_word, t, 1);
 
           mbar_wait(&bars->pds_full, t & 1, wc, 10);
+          TRACE(error_word, t, 2);
           // the previous column's dK / dV have been read out (S and dP of this tile did not need that)
           if (i == 0 && it_cnt >= 1) mbar_wait(&bars->acc_read, (it_cnt - 1) & 1, wc, 7);
           tc_fence_after();
@@ -416,6 +426,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
                      make_sdesc(aK + ks * 2048, kSub, 1024), id_dq, ks > 0);
           }
           if (leader) umma_commit(&bars->dq_full);
+          TRACE(error_word, t, 3);
           if (Cfg::kOwnStage) issue_dv();
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
@@ -423,6 +434,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
                      id_acc, (i > 0 || ks > 0));
           }
           if (leader) umma_commit(&bars->qd_empty[st]);
+          TRACE(error_word, t, 4);
           if (i == nt - 1) { if (leader) umma_commit(&bars->acc_full); if (leader) umma_commit(&bars->kv_free[kb]); }
         }
         ++it_cnt;
@@ -500,14 +512,14 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
           *reinterpret_cast<uint4*>(sK + kb * Cfg::kOperand + s * kSub + rr * 128 + ch * 16) = make_uint4(0, 0, 0, 0);
         }
         fence_proxy_async();
-        mbar_arrive(&bars->k_fix);
+        mbar_arrive_warp(&bars->k_fix);
         mbar_wait(&bars->v_full[kb], ku & 1, wc, 12);
         for (int i = pt; i < dead * 8 * Cfg::kSubs; i += 128) {
           const int s = i / (dead * 8), rr = c.keys + (i % (dead * 8)) / 8, ch = i % 8;
           *reinterpret_cast<uint4*>(sV + kb * Cfg::kOperand + s * kSub + rr * 128 + ch * 16) = make_uint4(0, 0, 0, 0);
         }
         fence_proxy_async();
-        mbar_arrive(&bars->v_fix);
+        mbar_arrive_warp(&bars->v_fix);
       }
       const int32_t* rows_i = ix.row_indices + (size_t)c.kv_row * ix.capacity + c.lo;
       const int32_t* heads_i = ix.head_indices + (size_t)c.kv_row * ix.capacity + c.lo;
@@ -526,6 +538,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         }
         if (e + kTile < c.n) { n_row = rows_i[e + kTile]; n_head = heads_i[e + kTile]; n_slot = slots_i[e + kTile]; }
         if (us >= 1) mbar_wait(&bars->qd_empty[st], (us - 1) & 1, wc, 13);
+        TRACE(error_word, t, 0);
         bars->meta[st][pt] = mt;
         bars->row_off[pt] = off;
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -542,12 +555,14 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
           cp_async16_hint(stage_g + o, dout + eo, ro < 0 ? 0u : 16u, keep);
         }
         cp_async_commit();
+        TRACE(error_word, t, 1);
         asm volatile("bar.sync 1, 128;" ::: "memory");
         // Published as soon as it has landed: these warps have nothing else to do until the
         // next stage frees, and a tile held back until then costs the MMA warp a wait.
         cp_async_wait<0>();
         fence_proxy_async();
-        mbar_arrive(&bars->qd_full[st]);
+        mbar_arrive_warp(&bars->qd_full[st]);
+        TRACE(error_word, t, 2);
       }
       ++it_cnt;
     }
@@ -642,14 +657,14 @@ int launch_one(const moba_b200_problem& p, const CUtensorMap& km, const CUtensor
                const void* dout, const float* lse, const float* delta, const moba_b200_index& ix,
                const int32_t* cu, void* dq_part, float* dkv_scratch, void* dk, void* dv, int n_items, unsigned* err,
                cudaStream_t st) {
-  auto kern = bwd_sm100_kernel<D, T>;
-  MOBA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<D>::kSmem));
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = n_items < sms ? n_items : sms;
   {
     KernelTimer timer__("bwd_sm100_kernel", st);
+    auto kern = bwd_sm100_kernel<D, T>;
+    MOBA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<D>::kSmem));
     kern<<<grid, kThreads, BwdCfg<D>::kSmem, st>>>(km, vm, (const T*)q, (const T*)dout, lse, delta, ix, cu,
                                                     (T*)dq_part, dkv_scratch, (T*)dk, (T*)dv, p, n_items, err);
     MOBA_LAUNCH_OK("bwd_sm100_kernel");

@@ -194,7 +194,7 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     mbar_init(&bars->q_full, 1); mbar_init(&bars->q_free, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->kb_full[i], 1); mbar_init(&bars->kb_empty[i], 1);
-      mbar_init(&bars->s_full[i], 1); mbar_init(&bars->s_free[i], 256);
+      mbar_init(&bars->s_full[i], 1); mbar_init(&bars->s_free[i], 8);
     }
     mbar_init(&bars->drain, 1);
     bars->abort = 0;
@@ -278,7 +278,7 @@ gate_sm100_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         for (int h = 0; h < 2; ++h) {
           tmem_ld32(tmem + lane_off + st * 128 + wg * 64 + h * 32, v);
           tmem_ld_wait();
-          if (h == 1) { tc_fence_before(); mbar_arrive(&bars->s_free[st]); }   // the scores are in registers
+          if (h == 1) { tc_fence_before(); mbar_arrive_warp(&bars->s_free[st]); }   // the scores are in registers
           // which of these 32 blocks are candidates of the tile: all, none, or some
           const int g0 = c0 + h * 32;
           const bool none = g0 >= u.tile || (p.gate_window > 0 && g0 >= p.gate_sinks && g0 + 32 <= u.tile - p.gate_window);

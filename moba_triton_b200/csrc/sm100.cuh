@@ -34,6 +34,13 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One arrival for a whole warp: every lane has done its own writes and fences; the warp
+// barrier orders them before lane 0's (releasing) arrival. 32 arrivals on one barrier word
+// would be 32 serialised shared-memory atomics.
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
@@ -72,6 +79,20 @@ struct WaitCtx {
 #else
 #define PHASE_CLOCK(t) do {} while (0)
 #define PHASE_ADD(ctx, site, t) do {} while (0)
+#endif
+
+// Trace builds (MOBA_TRACE) record the clock of lane 0 of every warp of CTA 0 at numbered
+// points of eight consecutive tiles, behind the wait counters of the device error buffer.
+#ifdef MOBA_TRACE
+constexpr int kTraceT0 = 20;
+constexpr int kTraceWordOffset = 64 + 2 * 32 * 160;
+#define TRACE(err, tile, ev)                                                                   \
+  do {                                                                                         \
+    if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (int)(tile) >= kTraceT0 && (int)(tile) < kTraceT0 + 8) \
+      reinterpret_cast<unsigned long long*>((err) + kTraceWordOffset)[(((int)(tile) - kTraceT0) * 32 + (threadIdx.x >> 5)) * 16 + (ev)] = clock64(); \
+  } while (0)
+#else
+#define TRACE(err, tile, ev) do {} while (0)
 #endif
 
 constexpr long long kWaitCycles = 1ll << 31;   // about a second of SM clock
@@ -159,6 +180,17 @@ __device__ __forceinline__ void st_global_stream16(void* dst, const uint4& w) {
 }
 __device__ __forceinline__ void st_global_stream_f32(float* dst, float v) {
   asm volatile("st.global.cs.f32 [%0], %1;" ::"l"(dst), "f"(v) : "memory");
+}
+
+// Bulk copy shared -> global (both 16-byte aligned, size a multiple of 16) by the copy engine;
+// the issuing thread groups its copies and waits until they have read their source.
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
 
 // Asks the L2 to fetch [p, p + bytes) (both multiples of 16); nothing waits for it.

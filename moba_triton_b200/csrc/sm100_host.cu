@@ -71,8 +71,8 @@ int encode_kbar_map_impl(CUtensorMap* out, const void* base, uint64_t kv_rows, u
 }
 
 // one word per device of this process, zero-initialised with the module
-#ifdef MOBA_WAIT_STATS
-__device__ unsigned g_error_word[64 + 2 * 32 * 160];      // debug builds: + per-CTA wait counters
+#if defined(MOBA_WAIT_STATS) || defined(MOBA_TRACE)
+__device__ unsigned g_error_word[64 + 2 * 32 * 160 + 2 * 8 * 32 * 16];   // debug builds: + per-CTA wait counters + trace
 #else
 __device__ unsigned g_error_word[1];
 #endif
@@ -90,6 +90,15 @@ unsigned* device_error_word() {
   }
   return table[dev];
 }
+
+#ifdef MOBA_TRACE
+extern "C" int moba_b200_debug_trace(unsigned long long* host_out) {
+  unsigned* base = device_error_word();
+  if (base == nullptr) return -1;
+  cudaDeviceSynchronize();
+  return (int)cudaMemcpy(host_out, base + 64 + 2 * 32 * 160, (size_t)8 * 32 * 16 * 8, cudaMemcpyDeviceToHost);
+}
+#endif
 
 #ifdef MOBA_WAIT_STATS
 extern "C" int moba_b200_debug_stats(unsigned long long* host_out, int n_ctas) {
