@@ -581,10 +581,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
 
 // dK / dV of the columns that were cut into several work items. CTA (x, y) looks at 256
 // consecutive work items of one (sequence, kv head) row, one per thread, and of the first
-// items of split columns it finds there takes every kReduceSlices-th, starting at y: it adds
-// the column's float32 partials in item order and stores the result. Split columns are the
-// heaviest ones and therefore neighbours in the dispatch order, hence the slicing; most CTAs
-// find nothing and leave.
+// items of split columns it finds there takes every kReduceSlices-th, starting at y, and of
+// each such column the z-th part of its sums: it adds the column's float32 partials in item
+// order and stores the result. Split columns are the heaviest ones and therefore neighbours in
+// the dispatch order, hence the slicing; most CTAs find nothing and leave.
 constexpr int kReduceSlices = 16;
 template <int D, typename T>
 __global__ void __launch_bounds__(256)
@@ -622,7 +622,7 @@ dkv_reduce_kernel(const float* __restrict__ dkv_scratch, moba_b200_index ix, con
     const int keys = min(kTile, sp.bos + sp.len - key0);
     constexpr int V4 = D / 4;                              // float4 per row
     constexpr int kAhead = 4;                              // elements per thread in flight
-    for (int i0 = threadIdx.x; i0 < 2 * kTile * V4; i0 += 256 * kAhead) {
+    for (int i0 = (int)blockIdx.z * 256 * kAhead + threadIdx.x; i0 < 2 * kTile * V4; i0 += 256 * kAhead * (int)gridDim.z) {
       float4 acc[kAhead];
 #pragma unroll
       for (int u = 0; u < kAhead; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -671,7 +671,8 @@ int launch_one(const moba_b200_problem& p, const CUtensorMap& km, const CUtensor
   }
   KernelTimer timer__("dkv_reduce_kernel", st);
   const int ctas_per_row = (ix.items_per_row + 255) / 256;
-  dkv_reduce_kernel<D, T><<<dim3(ctas_per_row * p.n_seq * p.kv_heads, kReduceSlices), 256, 0, st>>>(
+  // z: the 2 x 128 x D sums of a column in parts of 1024 float4, one per CTA
+  dkv_reduce_kernel<D, T><<<dim3(ctas_per_row * p.n_seq * p.kv_heads, kReduceSlices, D / 16), 256, 0, st>>>(
       dkv_scratch, ix, cu, (T*)dk, (T*)dv, p, ctas_per_row);
   MOBA_LAUNCH_OK("dkv_reduce_kernel");
   return MOBA_B200_OK;

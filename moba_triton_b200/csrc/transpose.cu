@@ -185,11 +185,17 @@ offsets_order_kernel(const int32_t* __restrict__ col_nnz, int32_t* __restrict__ 
   if (i < nb && part == 0) ord[rank] = i;
 }
 
-// One CTA per (sequence, kv head) row: the row's work items. Columns are taken in dispatch
-// order (longest first); a column of more than `tc` tiles becomes ceil(tiles / tc) items,
-// each with a dK/dV partial slot of its own. The slots of a row are consecutive and claimed
-// from a counter, so rows may claim in any order: slot numbers name scratch memory, results
-// do not depend on them.
+// One CTA per (sequence, kv head) row: the row's work items, largest first. A column of more
+// than `tc` tiles becomes ceil(tiles / tc) items, each with a dK/dV partial slot of its own:
+// pieces of `tc` tiles and a last, shorter one. The kernels deal the list out to their CTAs in
+// alternating direction, which balances a list that is sorted by size; so the full pieces come
+// first and the last pieces of the cut columns are merged, by size, into the (already sorted)
+// uncut columns: without that a CTA's share was off by up to 18 % when a CTA gets only some
+// eight items. The slots of a row are consecutive and claimed from a counter, so rows may
+// claim in any order: slot numbers name scratch memory, results do not depend on them, nor on
+// the order of the list. A row with more than kMaxCut cut columns keeps its columns' pieces
+// side by side, in column order (it has items enough for the order not to matter).
+constexpr int kMaxCut = 2048;
 __global__ void __launch_bounds__(1024)
 work_items_kernel(const int32_t* __restrict__ col_nnz, const int32_t* __restrict__ order, int4* __restrict__ items,
                   int32_t* __restrict__ slot_counter, int nb, int items_per_row, int tc, int slot_cap,
@@ -197,16 +203,18 @@ work_items_kernel(const int32_t* __restrict__ col_nnz, const int32_t* __restrict
   __shared__ long long warp_sums[32];
   __shared__ long long carry_s;
   __shared__ int base_s;
+  __shared__ int rem_s[kMaxCut], rank_s[kMaxCut], sorted_s[kMaxCut], slot_s[kMaxCut];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int32_t* nnz = col_nnz + (size_t)blockIdx.x * nb;
   const int32_t* ord = order + (size_t)blockIdx.x * nb;
   int4* out = items + (size_t)blockIdx.x * items_per_row;
+  auto tiles_of = [&](int r) { return (nnz[ord[r]] + 127) / 128; };
   auto chunks_of = [&](int r, int& blk, int& tiles) {
     blk = ord[r];
     tiles = (nnz[blk] + 127) / 128;
     return tiles <= tc ? 1 : (tiles + tc - 1) / tc;
   };
-  // (items, partial slots) of the row, summed as one 64-bit pair
+  // exclusive prefix of a 64-bit value over the CTA, and the CTA's total
   auto block_scan = [&](long long v, long long& total) {
     long long incl = v;
 #pragma unroll
@@ -226,23 +234,92 @@ work_items_kernel(const int32_t* __restrict__ col_nnz, const int32_t* __restrict
     total = all;
     return before + incl - v;
   };
-  // pass 1: how many partial slots the row needs
+  // pass 1: cut columns (a prefix of the dispatch order) and the partial slots the row needs
   long long mine = 0;
   for (int r = threadIdx.x; r < nb; r += 1024) {
     int blk, tiles;
     const int c = chunks_of(r, blk, tiles);
-    mine += (c > 1) ? c : 0;
+    if (c > 1) mine += 1LL | ((long long)c << 32);
   }
-  long long row_slots;
-  block_scan(mine, row_slots);
+  long long row_total;
+  block_scan(mine, row_total);
+  const int n_cut = (int)(row_total & 0xffffffffLL);
+  const int row_slots = (int)(row_total >> 32);
   if (threadIdx.x == 0) {
-    base_s = row_slots > 0 ? atomicAdd(slot_counter, (int)row_slots) : 0;
+    base_s = row_slots > 0 ? atomicAdd(slot_counter, row_slots) : 0;
     carry_s = 0;
-    if (row_slots > 0 && base_s + row_slots > slot_cap) atomicOr(error_word, 2u);   // sizes were promised by the host
+    if (row_slots > 0 && (long long)base_s + row_slots > slot_cap) atomicOr(error_word, 2u);   // sizes were promised by the host
   }
   __syncthreads();
   const int base = base_s;
-  // pass 2: place the items
+  // beyond the promised capacity (flagged above) an item falls back to "whole column": wrong
+  // sums, reported through the error word, but no access outside the scratch
+  auto slot_or_none = [&](int s) { return s < slot_cap ? s : -1; };
+  auto put = [&](int at, int4 it) {
+    if (at >= 0 && at < items_per_row) out[at] = it;
+    else atomicOr(error_word, 2u);
+  };
+
+  if (n_cut <= kMaxCut) {
+    const int n_full = row_slots - n_cut;                   // pieces of exactly tc tiles: they lead the list
+    // the cut columns: full pieces in column order, the last piece's size and slot for later
+    for (int r0 = 0; r0 < n_cut; r0 += 1024) {
+      const int r = r0 + threadIdx.x;
+      int blk = 0, tiles = 0, c = 0;
+      if (r < n_cut) c = chunks_of(r, blk, tiles);
+      long long total;
+      const long long carry = carry_s;
+      const int slot0 = (int)(carry + block_scan((long long)c, total));   // pieces of the cut columns before this one
+      if (r < n_cut) {
+        const int full0 = slot0 - r;                        // each earlier cut column has one piece that is not full
+        for (int i = 0; i + 1 < c; ++i) put(full0 + i, make_int4(blk, i * tc, tc, slot_or_none(base + slot0 + i)));
+        rem_s[r] = tiles - (c - 1) * tc;
+        slot_s[r] = slot0;
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) carry_s = carry + total;
+      __syncthreads();
+    }
+    // rank of each last piece among the last pieces: larger first, ties in column order
+    for (int r = threadIdx.x; r < n_cut; r += 1024) {
+      const int mine_rem = rem_s[r];
+      int rank = 0;
+      for (int q = 0; q < n_cut; ++q) {
+        const int o = rem_s[q];
+        rank += (o > mine_rem || (o == mine_rem && q < r)) ? 1 : 0;
+      }
+      rank_s[r] = rank;
+      sorted_s[rank] = mine_rem;
+    }
+    __syncthreads();
+    // last pieces of the cut columns: behind the uncut columns that are larger
+    for (int r = threadIdx.x; r < n_cut; r += 1024) {
+      const int mine_rem = rem_s[r];
+      int lo = n_cut, hi = nb;                              // first uncut column with tiles <= mine_rem
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (tiles_of(mid) > mine_rem) lo = mid + 1; else hi = mid;
+      }
+      int blk, tiles;
+      const int c = chunks_of(r, blk, tiles);
+      put(n_full + rank_s[r] + (lo - n_cut), make_int4(blk, (c - 1) * tc, mine_rem, slot_or_none(base + slot_s[r] + c - 1)));
+    }
+    // uncut columns: behind the last pieces that are at least as large
+    for (int r = n_cut + threadIdx.x; r < nb; r += 1024) {
+      int blk, tiles;
+      chunks_of(r, blk, tiles);
+      int lo = 0, hi = n_cut;                               // first last piece smaller than this column
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (sorted_s[mid] >= tiles) lo = mid + 1; else hi = mid;
+      }
+      put(n_full + (r - n_cut) + lo, make_int4(blk, 0, tiles, -1));
+    }
+    for (int j = n_full + nb + threadIdx.x; j < items_per_row; j += 1024) out[j] = make_int4(0, 0, 0, -2);   // padding
+    return;
+  }
+
+  // more cut columns than the tables hold: each column's pieces side by side, in column order
   for (int r0 = 0; r0 < nb; r0 += 1024) {
     const int r = r0 + threadIdx.x;
     int blk = 0, tiles = 0, c = 0;
@@ -252,13 +329,8 @@ work_items_kernel(const int32_t* __restrict__ col_nnz, const int32_t* __restrict
     const long long carry = carry_s;
     const long long at = carry + block_scan(v, total);
     const int item0 = (int)(at & 0xffffffffLL), slot0 = (int)(at >> 32);
-    for (int i = 0; i < c; ++i) {
-      if (item0 + i >= items_per_row) { atomicOr(error_word, 2u); break; }
-      // beyond the promised capacity (flagged above) an item falls back to "whole column":
-      // wrong sums, reported through the error word, but no access outside the scratch
-      const int slot = (c > 1 && base + slot0 + i < slot_cap) ? base + slot0 + i : -1;
-      out[item0 + i] = make_int4(blk, i * tc, tiles == 0 ? 0 : min(tc, tiles - i * tc), slot);
-    }
+    for (int i = 0; i < c; ++i)
+      put(item0 + i, make_int4(blk, i * tc, tiles == 0 ? 0 : min(tc, tiles - i * tc), c > 1 ? slot_or_none(base + slot0 + i) : -1));
     __syncthreads();
     if (threadIdx.x == 0) carry_s = carry + total;
     __syncthreads();

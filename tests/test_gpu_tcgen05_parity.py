@@ -212,10 +212,32 @@ def _work_item_invariants(index):
                 else:
                     assert total <= index.chunk_tiles
             assert torch.equal(covered, -(-nnz[si, h].long() // 128)), "every tile of every column exactly once"
-            # dispatch order: heaviest column first
+            # dispatch order: heaviest column first, and the list as a whole sorted by size
             first_items = it[it[:, 1] == 0][:, 0].long()
             assert torch.equal(first_items, index.order[si, h].cpu().long())
+            assert bool((it[:-1, 2] >= it[1:, 2]).all()), "work items must be listed largest first"
     return len(slots_seen)
+
+
+def test_work_items_are_listed_largest_first(device):
+    """Columns cut at three tiles: pieces of three tiles lead the list, the shorter last pieces
+    are merged by size into the uncut columns (the kernels deal the list out in alternating
+    direction, which balances a sorted list)."""
+    old = _lib.set_chunk_tiles(3)
+    try:
+        cfg = moba.MoBAConfig(128, 4)
+        g = torch.Generator().manual_seed(77)
+        q = torch.randn((1, 4096, 4, 64), generator=g).to(torch.bfloat16).to(device)
+        k = torch.randn((1, 4096, 2, 64), generator=g).to(torch.bfloat16).to(device)
+        index = moba.build_csc_fused(q, k, cfg)
+        assert index.chunk_tiles == 3
+        assert _work_item_invariants(index) > 0
+        items = index.work_items.cpu()[0, 0]
+        items = items[items[:, 3] != -2]
+        sizes = items[:, 2].tolist()
+        assert sizes[0] == 3 and 0 < min(s for s in sizes if s) < 3, "the case must hold pieces of several sizes"
+    finally:
+        _lib.set_chunk_tiles(old)
 
 
 @pytest.mark.parametrize("d,hq,hkv,cu", [(64, 4, 2, None), (128, 4, 1, None), (64, 4, 2, [0, 640, 1000, 1664])],
