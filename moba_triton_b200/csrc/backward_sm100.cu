@@ -581,11 +581,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
 
 // dK / dV of the columns that were cut into several work items. CTA (x, y) looks at 256
 // consecutive work items of one (sequence, kv head) row, one per thread, and of the first
-// items of split columns it finds there takes every kReduceSlices-th, starting at y, and of
+// items of split columns it finds there takes every gridDim.y-th, starting at y, and of
 // each such column the z-th part of its sums: it adds the column's float32 partials in item
 // order and stores the result. Split columns are the heaviest ones and therefore neighbours in
 // the dispatch order, hence the slicing; most CTAs find nothing and leave.
-constexpr int kReduceSlices = 16;
+constexpr int kReduceSlices = 16;                       // at most; fewer when the rows give CTAs enough
 template <int D, typename T>
 __global__ void __launch_bounds__(256)
 dkv_reduce_kernel(const float* __restrict__ dkv_scratch, moba_b200_index ix, const int32_t* __restrict__ cu,
@@ -613,7 +613,7 @@ dkv_reduce_kernel(const float* __restrict__ dkv_scratch, moba_b200_index ix, con
   const int seq = kv_row / p.kv_heads, kvh = kv_row % p.kv_heads;
   const SeqSpan sp = seq_span(cu, p.packed, seq, p.tokens);
   const size_t b = p.packed ? 0 : (size_t)seq;
-  for (int f = blockIdx.y; f < n_found; f += kReduceSlices) {
+  for (int f = blockIdx.y; f < n_found; f += (int)gridDim.y) {
     const int4 col = found[f];
     const int nnz = ix.col_nnz[(size_t)kv_row * p.num_blocks + col.x];
     const int tiles = (nnz + kTile - 1) / kTile;
@@ -671,8 +671,14 @@ int launch_one(const moba_b200_problem& p, const CUtensorMap& km, const CUtensor
   }
   KernelTimer timer__("dkv_reduce_kernel", st);
   const int ctas_per_row = (ix.items_per_row + 255) / 256;
-  // z: the 2 x 128 x D sums of a column in parts of 1024 float4, one per CTA
-  dkv_reduce_kernel<D, T><<<dim3(ctas_per_row * p.n_seq * p.kv_heads, kReduceSlices, D / 16), 256, 0, st>>>(
+  // z: the 2 x 128 x D sums of a column in parts of at least 1024 float4; fewer parts when the
+  // rows alone give CTAs enough (every CTA first looks through its 256 items)
+  const int x_ctas = ctas_per_row * p.n_seq * p.kv_heads;
+  int slices = 4096 / x_ctas;
+  slices = slices < 1 ? 1 : (slices > kReduceSlices ? kReduceSlices : slices);
+  int parts = 4096 / (x_ctas * slices);
+  parts = parts < 1 ? 1 : (parts > D / 16 ? D / 16 : parts);
+  dkv_reduce_kernel<D, T><<<dim3(x_ctas, slices, parts), 256, 0, st>>>(
       dkv_scratch, ix, cu, (T*)dk, (T*)dv, p, ctas_per_row);
   MOBA_LAUNCH_OK("dkv_reduce_kernel");
   return MOBA_B200_OK;
