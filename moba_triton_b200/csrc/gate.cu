@@ -48,8 +48,8 @@ pool_kernel(const T* __restrict__ k, const int32_t* __restrict__ cu, T* __restri
 #pragma unroll
   for (int e = 0; e < EPV; ++e) acc[e] = 0.0;
   if (rg < groups) {
-    // eight rows in flight per thread: the loads do not depend on one another
-    constexpr int kAhead = 8;
+    // four rows in flight per thread: the loads do not depend on one another
+    constexpr int kAhead = 4;
     for (int r0 = rg; r0 < hi - lo; r0 += groups * kAhead) {
       uint4 raw[kAhead];
 #pragma unroll
@@ -67,19 +67,18 @@ pool_kernel(const T* __restrict__ k, const int32_t* __restrict__ cu, T* __restri
       }
     }
   }
+  // Sums over the row groups, one output element per thread (float64 sums of these values are
+  // exact, so the order of the additions does not matter).
   __shared__ double red[128 * EPV];
 #pragma unroll
   for (int e = 0; e < EPV; ++e) red[threadIdx.x * EPV + e] = acc[e];
   __syncthreads();
-  if (threadIdx.x < vpr) {
-    const float occ = (float)(hi - lo);
-#pragma unroll
-    for (int e = 0; e < EPV; ++e) {
-      double s = 0.0;
-      for (int g = 0; g < groups; ++g) s += red[(g * vpr + threadIdx.x) * EPV + e];
-      const float total = Elem<T>::round_f((float)s);
-      dst[threadIdx.x * EPV + e] = Elem<T>::from_f(__fdiv_rn(total, occ));
-    }
+  const float occ = (float)(hi - lo);
+  for (int i = threadIdx.x; i < d; i += 128) {
+    double s = 0.0;
+    for (int g = 0; g < groups; ++g) s += red[g * d + i];       // thread g * vpr + i / EPV, element i % EPV
+    const float total = Elem<T>::round_f((float)s);
+    dst[i] = Elem<T>::from_f(__fdiv_rn(total, occ));
   }
 }
 
