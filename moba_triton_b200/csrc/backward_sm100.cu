@@ -556,6 +556,19 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         }
         cp_async_commit();
         TRACE(error_word, t, 1);
+        if (NST == 1 && e + kTile < c.n) {
+          // With one stage the copies of the next tile's rows cannot start before this tile's
+          // last MMA has retired, and the MMA warp then waits for them. The rows are asked into
+          // the L2 now (the index entry has arrived while this tile's copies were issued), so
+          // that those copies find them there instead of in DRAM. With two stages the copies
+          // run a tile ahead anyway and the extra requests only cost (0.72 -> 0.73 ms at D=64).
+          const size_t nxt = ((c.b * p.tokens + n_row) * p.q_heads + n_head) * (size_t)D;
+#pragma unroll
+          for (int line = 0; line < D * 2 / 128; ++line) {
+            l2_prefetch_line(q + nxt + line * 64);
+            l2_prefetch_line(dout + nxt + line * 64);
+          }
+        }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         // Published as soon as it has landed: these warps have nothing else to do until the
         // next stage frees, and a tile held back until then costs the MMA warp a wait.

@@ -197,6 +197,11 @@ __device__ __forceinline__ void bulk_wait_read() {
 __device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) {
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
+// Asks the L2 for the 128-byte line that holds `p` (an ordinary load-store-unit request: cheap
+// to issue, unlike the bulk form above, which goes through the copy engine one request at a time).
+__device__ __forceinline__ void l2_prefetch_line(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p) : "memory");
+}
 // Prefetches elements [lo, lo + n) of an int32 array of `total` elements.
 __device__ __forceinline__ void l2_prefetch_i32(const int32_t* base, size_t lo, int n, size_t total) {
   const size_t b0 = (lo * 4) & ~size_t(15);
