@@ -64,11 +64,11 @@ struct Bars {
   uint64_t q_full[4];                      // per buffer: the warpgroup's gathered Q tile has landed
   uint64_t q_empty[4];                     // per stage: the S MMA that read it has retired
   uint64_t s_full[4], p_full[4], o_full[4], so_free[4];
-  uint64_t col_full[4];                    // column descriptors published by the loader
+  uint64_t col_full[8];                    // column descriptors published by the loader
   uint64_t drain[2];                       // all MMAs of an issuing thread have completed
   uint32_t tmem_base;
   int abort;
-  Column cols[4];                          // ring: cols[i & 3] describes the CTA's i-th column; n < 0 ends the stream
+  Column cols[8];                          // ring: cols[i & 7] describes the CTA's i-th column; n < 0 ends the stream
   unsigned char* out_ptr[4][kTile];        // destination rows of the tile each warpgroup is storing
   int q_row[4][2][kTile];                  // per warpgroup, two gathers deep: row of the [B*T*Hq][D] view of q, -1 = none
 };
@@ -168,8 +168,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       mbar_init(&bars->q_full[i], 4); mbar_init(&bars->q_empty[i], 1);
       mbar_init(&bars->s_full[i], 1); mbar_init(&bars->p_full[i], 4);
       mbar_init(&bars->o_full[i], 1); mbar_init(&bars->so_free[i], 4);
-      mbar_init(&bars->col_full[i], 1);
     }
+    for (int i = 0; i < 8; ++i) mbar_init(&bars->col_full[i], 1);
     mbar_init(&bars->drain[0], 1); mbar_init(&bars->drain[1], 1);
     bars->abort = 0;
     fence_barrier_init();
@@ -202,11 +202,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
     auto locate = [&](Cur& k, bool blocking) -> int {
       for (;;) {
         if (!k.have) {
-          bool ok = blocking ? mbar_wait(&bars->col_full[k.it & 3], (k.it >> 2) & 1, wc, 1)
-                             : mbar_try_wait(&bars->col_full[k.it & 3], (k.it >> 2) & 1);
+          bool ok = blocking ? mbar_wait(&bars->col_full[k.it & 7], (k.it >> 3) & 1, wc, 1)
+                             : mbar_try_wait(&bars->col_full[k.it & 7], (k.it >> 3) & 1);
           ok = group_all(ok, bar_id);
           if (!ok) return blocking ? 0 : -1;
-          k.c = bars->cols[k.it & 3];
+          k.c = bars->cols[k.it & 7];
           if (k.c.n < 0) return 0;
           k.nt = (k.c.n + kTile - 1) / kTile;
           k.have = true;
@@ -414,11 +414,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       const bool is_s = warp == Cfg::kMmaWarp;
       uint32_t t = 0, pt = 0;                                   // tiles issued, cut-short columns seen
       for (uint32_t it = 0;; ++it) {
-        if (!mbar_wait(&bars->col_full[it & 3], (it >> 2) & 1, wc, 20)) break;
-        const int n = bars->cols[it & 3].n;
+        if (!mbar_wait(&bars->col_full[it & 7], (it >> 3) & 1, wc, 20)) break;
+        const int n = bars->cols[it & 7].n;
         if (n < 0) break;
         const int nt = (n + kTile - 1) / kTile;
-        const bool partial = bars->cols[it & 3].keys < kTile;
+        const bool partial = bars->cols[it & 7].keys < kTile;
         for (int i = 0; i < nt; ++i, ++t) {
           const uint32_t b = t % NB, u = t / NB;
           if (is_s) {
@@ -493,19 +493,34 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         l2_prefetch_i32(arr, (size_t)c.kv_row * ix.capacity + c.lo, c.n, index_elems);
       }
     };
-    prefetch_entries(0);
-    for (int round = 0; round * G < n_items; ++round) {
-      prefetch_entries(round + 1);
-      const int item = item_of(round);
-      if (item >= n_items) continue;
-      Column c;
-      if (!load_column(c, item, ix, p, cu, n_kv_rows)) continue;
-      if (*wc.abort) break;                                 // no new loads once a wait gave up
+    // The next item with pairs at or after `round` (its round is returned, -1 at the end).
+    auto find = [&](Column& c, int round) {
+      for (; round * G < n_items; ++round) {
+        const int item = item_of(round);
+        if (item < n_items && load_column(c, item, ix, p, cu, n_kv_rows)) return round;
+      }
+      return -1;
+    };
+    // Descriptor number `n` of the stream. The ring holds eight and the descriptors run one
+    // item ahead of the K/V loads: a descriptor is overwritten when the MMAs of the item five
+    // places behind it have long retired.
+    auto publish = [&](const Column& c, uint32_t n) {
       __syncwarp();
       if (lane == 0) {
-        bars->cols[it_cnt & 3] = c;
-        mbar_arrive(&bars->col_full[it_cnt & 3]);
+        bars->cols[n & 7] = c;
+        mbar_arrive(&bars->col_full[n & 7]);
       }
+    };
+    Column c, c_next;
+    int round = find(c, 0);
+    if (round >= 0) { prefetch_entries(round); publish(c, 0); }
+    while (round >= 0) {
+      // The softmax warps look for their next tile while they work on the current one; at the
+      // last tiles of an item that is a tile of the next item, so its descriptor (and, in the
+      // L2, its index entries) must be there before this item's K and V are even loaded.
+      const int round_next = find(c_next, round + 1);
+      if (round_next >= 0) { prefetch_entries(round_next); publish(c_next, it_cnt + 1); }
+      if (*wc.abort) break;                                 // no new loads once a wait gave up
       const int kvh = c.kv_row % p.kv_heads;
       const int tok0 = (int)(c.b * p.tokens) + c.key0;
       if (it_cnt >= 1) mbar_wait(&bars->k_free, (it_cnt - 1) & 1, wc, 4);
@@ -536,11 +551,13 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         mbar_arrive_warp(&bars->v_fix);
       }
       ++it_cnt;
+      c = c_next;
+      round = round_next;
     }
     __syncwarp();
     if (lane == 0) {
-      bars->cols[it_cnt & 3].n = -1;                          // end of the stream
-      mbar_arrive(&bars->col_full[it_cnt & 3]);
+      bars->cols[it_cnt & 7].n = -1;                          // end of the stream
+      mbar_arrive(&bars->col_full[it_cnt & 7]);
       // No load may be in flight into this CTA's shared memory when it exits.
       if (it_cnt >= 1) {
         mbar_wait_quiet(&bars->k_full, (it_cnt - 1) & 1);
