@@ -4,24 +4,28 @@
 // Persistent CTAs (one per SM) walk the (sequence, kv head, block) columns in
 // longest-first order, round-robin. Work is cut into tiles of 128 gathered
 // queries; NB tiles (4 at head_dim 64, 2 at 128) are in flight per SM, each on
-// its own TMEM buffer, P buffer and softmax warpgroup, because one tile is a
-// long chain of short dependent steps (gather -> MMA -> softmax -> MMA ->
+// its own TMEM buffer, output staging tile and softmax warpgroup, because one tile
+// is a long chain of short dependent steps (gather -> MMA -> softmax -> MMA ->
 // epilogue) and only several chains side by side keep the SM busy.
-//   loader   (1 warp)    walks the work list, publishes each column's descriptor in
-//                        shared memory, TMA-loads its K block and V block; zeroes the
-//                        rows of a block that its sequence cuts short
+//   loader   (1 warp)    walks the work list, publishes each item's descriptor in shared
+//                        memory one item ahead of its loads, TMA-loads its K block and V
+//                        block (two buffers each at head_dim 64); zeroes the rows of a
+//                        block that its sequence cuts short
 //   mma      (2 threads) one issues S = Q K^T (M128 N128 K=D) tile after tile, the other
-//                        O = P V (M128 N=D K128), written over the first D columns of the
-//                        same TMEM buffer; each blocks on what its next tile needs, so a
-//                        tile that becomes ready is issued without a polling round
+//                        O = P V (M128 N=D K128) with P as operand A **from TMEM**; each
+//                        blocks on what its next tile needs, so a tile that becomes ready
+//                        is issued without a polling round
 //   softmax  (NB x 4 warps; warpgroup w owns tiles t = w mod NB)
 //            - gathers the 128 query rows of its *next* tile with 16-byte asynchronous
 //              copies, issued between the two passes over the current tile's scores: a
 //              warp sustains only about 3 bytes per clock of such copies, so the copying
 //              is spread over all 4 NB warps instead of a few dedicated ones;
-//            - tcgen05.ld S, mask, exp2, row sum, P (16-bit) -> smem; then tcgen05.ld O,
+//            - tcgen05.ld S, mask, exp2, row sum, P (16-bit pairs) -> tcgen05.st over the
+//              scores already read (P never touches shared memory); then tcgen05.ld O,
 //              normalise, stage in smem and store the partial output rows (eight or
 //              sixteen lanes per row) and their log2-sum-exp at the (query, slot) addresses
+// TMEM columns of a buffer: S [0,128), P over [0,64), O in [64,128) at head_dim 64 and in
+// a second 128 columns at head_dim 128.
 // A (query, block) pair is complete inside one tile, so nothing is rescaled
 // here; the merge kernel combines a query's slots.
 //
@@ -47,8 +51,13 @@ template <int D> struct FwdCfg {
   // Q stages form a ring over the CTA's tile sequence (tile t lives in stage t mod kQStages);
   // shared memory has no room for one stage per buffer at head_dim 64.
   static constexpr int kQStages = tensor_core_plan(D).fwd_q_stages;
-  static constexpr int kPBytes = 2 * kSub;             // [128][128] 16-bit
-  static constexpr int kSmemData = 2 * kOperand + kQStages * kOperand + kBufs * kPBytes;
+  // P never goes through shared memory: it is written back to TMEM over the scores it was
+  // computed from and read from there as operand A of P V. What each tile in flight keeps in
+  // shared memory is a staging tile for its 16-bit output rows.
+  static constexpr int kStageBytes = kOperand;         // [128][D] 16-bit
+  // K and V buffers: with two, the next item's blocks load while this item's last tiles run.
+  static constexpr int kKvBufs = (D == 64) ? 2 : 1;
+  static constexpr int kSmemData = 2 * kKvBufs * kOperand + kQStages * kOperand + kBufs * kStageBytes;
   static constexpr int kSmem = kSmemData + 1024 /*align*/ + 10240 /*barriers, row tables*/;
   static constexpr int kMmaWarp = 4 * kBufs, kPvWarp = kMmaWarp + 1, kLoadWarp = kMmaWarp + 2;
   static constexpr int kThreads = (4 * kBufs + 3) * 32;
@@ -60,7 +69,7 @@ struct Column {                            // one unit of work
 };
 
 struct Bars {
-  uint64_t k_full, v_full, k_fix, v_fix, k_free, v_free;
+  uint64_t k_full[2], v_full[2], k_free[2], v_free[2], k_fix, v_fix;
   uint64_t q_full[4];                      // per buffer: the warpgroup's gathered Q tile has landed
   uint64_t q_empty[4];                     // per stage: the S MMA that read it has retired
   uint64_t s_full[4], p_full[4], o_full[4], so_free[4];
@@ -139,14 +148,14 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
                  TP* __restrict__ part_o, float* __restrict__ part_lse, moba_b200_problem p, int n_items,
                  unsigned* error_word) {
   using Cfg = FwdCfg<D>;
-  constexpr int NQ = Cfg::kQStages, NB = Cfg::kBufs;
+  constexpr int NQ = Cfg::kQStages, NB = Cfg::kBufs, NKV = Cfg::kKvBufs;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
-  unsigned char* sK = smem;
-  unsigned char* sV = sK + Cfg::kOperand;
-  unsigned char* sQ = sV + Cfg::kOperand;                       // NQ stages
-  unsigned char* sP = sQ + NQ * Cfg::kOperand;                  // NB buffers
-  Bars* bars = reinterpret_cast<Bars*>(sP + NB * Cfg::kPBytes);
+  unsigned char* sK = smem;                                     // NKV buffers
+  unsigned char* sV = sK + NKV * Cfg::kOperand;
+  unsigned char* sQ = sV + NKV * Cfg::kOperand;                 // NQ stages
+  unsigned char* sO = sQ + NQ * Cfg::kOperand;                  // NB output staging tiles
+  Bars* bars = reinterpret_cast<Bars*>(sO + NB * Cfg::kStageBytes);
   static_assert(sizeof(Bars) <= 10240, "barrier block outgrew its reservation");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -161,9 +170,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
 #endif
 
   if (threadIdx.x == 0) {
-    mbar_init(&bars->k_full, 1); mbar_init(&bars->v_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->k_full[i], 1); mbar_init(&bars->v_full[i], 1);
+      mbar_init(&bars->k_free[i], 1); mbar_init(&bars->v_free[i], 1);
+    }
     mbar_init(&bars->k_fix, 1); mbar_init(&bars->v_fix, 1);
-    mbar_init(&bars->k_free, 1); mbar_init(&bars->v_free, 1);
     for (int i = 0; i < 4; ++i) {
       mbar_init(&bars->q_full[i], 4); mbar_init(&bars->q_empty[i], 1);
       mbar_init(&bars->s_full[i], 1); mbar_init(&bars->p_full[i], 4);
@@ -189,8 +200,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
     const int wg = warp >> 2;                         // owns tiles with t % NB == wg and buffer wg
     const int r = (warp & 3) * 32 + lane;             // row of the tile == TMEM lane
     const int bar_id = 2 + wg;                        // named barrier of this warpgroup
-    const uint32_t tbuf = tmem + ((uint32_t)((warp & 3) * 32) << 16) + wg * 128;
-    unsigned char* myP = sP + wg * Cfg::kPBytes;
+    const uint32_t tbuf = tmem + ((uint32_t)((warp & 3) * 32) << 16) + wg * ((D == 64) ? 128 : 256);
+    unsigned char* myO = sO + wg * Cfg::kStageBytes;            // staging of this warpgroup's output rows
+    // TMEM columns of a buffer: scores [0, 128); P, 16-bit pairs, over [0, 64); O in [128 - D, 128)
+    // at head_dim 64 and in a second 128 columns at head_dim 128.
+    constexpr uint32_t kOCol = (D == 64) ? 64 : 128;
+    constexpr uint32_t kBufCols = (D == 64) ? 128 : 256;
     constexpr int CPR = D / 8;                        // 16-byte chunks per gathered row
     constexpr int RPP = 128 / CPR;                    // rows per pass of the warpgroup
 
@@ -314,7 +329,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         for (int ch = 0; ch < 4; ++ch) {
           tmem_ld32(tbuf + ch * 32, v);
           tmem_ld_wait();
-          unsigned char* dst_sub = myP + (ch >> 1) * kSub;
+          // P of these 32 keys goes back over scores that have been read: chunk ch's 16-bit
+          // pairs land in columns [16 ch, 16 ch + 16), all of them below column 32 (ch + 1).
+          uint32_t pk[16];
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             float pe[8];
@@ -325,18 +342,17 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
               else pe[k] = x;
               l4[k & 3] += pe[k];
             }
-            uint4 w;
-            w.x = pack2<T>(pe[0], pe[1]); w.y = pack2<T>(pe[2], pe[3]);
-            w.z = pack2<T>(pe[4], pe[5]); w.w = pack2<T>(pe[6], pe[7]);
-            *reinterpret_cast<uint4*>(dst_sub + swz128(r, (ch & 1) * 4 + g)) = w;
+            pk[g * 4 + 0] = pack2<T>(pe[0], pe[1]); pk[g * 4 + 1] = pack2<T>(pe[2], pe[3]);
+            pk[g * 4 + 2] = pack2<T>(pe[4], pe[5]); pk[g * 4 + 3] = pack2<T>(pe[6], pe[7]);
           }
+          tmem_st16(tbuf + ch * 16, pk);
         }
+        tmem_st_wait();
       };
       if (all_open) exp_pass(std::false_type{}); else exp_pass(std::true_type{});
       const float l = (l4[0] + l4[1]) + (l4[2] + l4[3]);
       PHASE_ADD(wc, 14, ph);                           // second pass (exp, P)
-      if (nxt == 1) cp_async_wait<0>();                // the next tile's rows have landed
-      fence_proxy_async();                             // P and those rows -> visible to the MMA
+      if (nxt == 1) { cp_async_wait<0>(); fence_proxy_async(); }   // the next tile's rows have landed and are visible to the MMA
       tc_fence_before();
       mbar_arrive_warp(&bars->p_full[wg]);
       if (nxt == 1) mbar_arrive_warp(&bars->q_full[wg]);
@@ -352,11 +368,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       PHASE_ADD(wc, 16, ph);                           // o_full wait
 #pragma unroll 1
       for (int ch = 0; ch < D / 32; ++ch) {
-        tmem_ld32(tbuf + ch * 32, v);
+        tmem_ld32(tbuf + kOCol + ch * 32, v);
         tmem_ld_wait();
         if (sizeof(TP) == 2) {
-          // Stage the 16-bit tile in this buffer's P region (its MMA has retired): one row
-          // per thread straight to global memory would touch 32 lines per instruction.
+          // Stage the 16-bit tile in shared memory: one row per thread straight to global
+          // memory would touch 32 lines per instruction.
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             uint4 w;
@@ -364,7 +380,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
             w.y = pack2<T>(__uint_as_float(v[g * 8 + 2]) * inv, __uint_as_float(v[g * 8 + 3]) * inv);
             w.z = pack2<T>(__uint_as_float(v[g * 8 + 4]) * inv, __uint_as_float(v[g * 8 + 5]) * inv);
             w.w = pack2<T>(__uint_as_float(v[g * 8 + 6]) * inv, __uint_as_float(v[g * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(myP + (ch >> 1) * kSub + swz128(r, (ch & 1) * 4 + g)) = w;
+            *reinterpret_cast<uint4*>(myO + (ch >> 1) * kSub + swz128(r, (ch & 1) * 4 + g)) = w;
           }
         } else if (live && o_ok) {
           float4* d4 = reinterpret_cast<float4*>(reinterpret_cast<unsigned char*>(dst) + ch * 128);
@@ -388,10 +404,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         for (int pass = 0; pass < CPRO; ++pass) {
           const int rr = pass * RPPO + r / CPRO;
           unsigned char* op = bars->out_ptr[wg][rr];
-          const uint4 w = *reinterpret_cast<const uint4*>(myP + (cc >> 3) * kSub + swz128(rr, cc & 7));
+          const uint4 w = *reinterpret_cast<const uint4*>(myO + (cc >> 3) * kSub + swz128(rr, cc & 7));
           if (op != nullptr) st_global_stream16(op + cc * 16, w);
         }
-        asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");   // the staging area is P again
+        asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");   // the staging tile may be written again
       }
       PHASE_ADD(wc, 18, ph);                           // partial rows stored
 
@@ -410,7 +426,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       constexpr uint32_t idesc_s = make_idesc(0, 128, 128, 0, 0);
       constexpr uint32_t idesc_o = make_idesc(0, 128, D, 0, 1);
       const uint32_t fbits = (fmt << 7) | (fmt << 10);
-      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), aP = smem_u32(sP);
+      const uint32_t aQ = smem_u32(sQ);
+      constexpr uint32_t kOCol = (D == 64) ? 64 : 128, kBufCols = (D == 64) ? 128 : 256;
       const bool is_s = warp == Cfg::kMmaWarp;
       uint32_t t = 0, pt = 0;                                   // tiles issued, cut-short columns seen
       for (uint32_t it = 0;; ++it) {
@@ -419,6 +436,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         if (n < 0) break;
         const int nt = (n + kTile - 1) / kTile;
         const bool partial = bars->cols[it & 7].keys < kTile;
+        const uint32_t kb = it % NKV, ku = it / NKV;             // K/V buffer of the item, its earlier uses
+        const uint32_t aK = smem_u32(sK) + kb * Cfg::kOperand, aV = smem_u32(sV) + kb * Cfg::kOperand;
         for (int i = 0; i < nt; ++i, ++t) {
           const uint32_t b = t % NB, u = t / NB;
           if (is_s) {
@@ -427,7 +446,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
             mbar_wait(&bars->q_full[b], u & 1, wc, 21);
             if (u >= 1) mbar_wait(&bars->so_free[b], (u - 1) & 1, wc, 22);
             if (i == 0) {
-              mbar_wait(&bars->k_full, it & 1, wc, 23);
+              mbar_wait(&bars->k_full[kb], ku & 1, wc, 23);
               if (partial) mbar_wait(&bars->k_fix, pt & 1, wc, 23);
             }
             tc_fence_after();
@@ -435,28 +454,28 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks) {
               const uint32_t o = (ks >> 2) * kSub + (ks & 3) * 32;
-              umma_f16(tmem + b * 128, make_sdesc(qb + o, 16, 1024), make_sdesc(aK + o, 16, 1024),
+              umma_f16(tmem + b * kBufCols, make_sdesc(qb + o, 16, 1024), make_sdesc(aK + o, 16, 1024),
                        idesc_s | fbits, ks > 0);
             }
             umma_commit(&bars->s_full[b]);
             umma_commit(&bars->q_empty[qs]);
-            if (i == nt - 1) umma_commit(&bars->k_free);
+            if (i == nt - 1) umma_commit(&bars->k_free[kb]);
           } else {
             // ---- O = P V of tile t ----
             mbar_wait(&bars->p_full[b], u & 1, wc, 24);
             if (i == 0) {
-              mbar_wait(&bars->v_full, it & 1, wc, 25);
+              mbar_wait(&bars->v_full[kb], ku & 1, wc, 25);
               if (partial) mbar_wait(&bars->v_fix, pt & 1, wc, 25);
             }
             tc_fence_after();
-            const uint32_t pb = aP + b * Cfg::kPBytes;
+            // operand A: P from TMEM, 16 keys (eight columns of 16-bit pairs) per step
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
-              umma_f16(tmem + b * 128, make_sdesc(pb + (ks >> 2) * kSub + (ks & 3) * 32, 16, 1024),
-                       make_sdesc(aV + ks * 2048, kSub, 1024), idesc_o | fbits, ks > 0);
+              umma_f16_ts(tmem + b * kBufCols + kOCol, tmem + b * kBufCols + ks * 8,
+                          make_sdesc(aV + ks * 2048, kSub, 1024), idesc_o | fbits, ks > 0);
             }
             umma_commit(&bars->o_full[b]);
-            if (i == nt - 1) umma_commit(&bars->v_free);
+            if (i == nt - 1) umma_commit(&bars->v_free[kb]);
           }
         }
         if (partial) ++pt;
@@ -523,29 +542,32 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       if (*wc.abort) break;                                 // no new loads once a wait gave up
       const int kvh = c.kv_row % p.kv_heads;
       const int tok0 = (int)(c.b * p.tokens) + c.key0;
-      if (it_cnt >= 1) mbar_wait(&bars->k_free, (it_cnt - 1) & 1, wc, 4);
+      const uint32_t kb = it_cnt % NKV, ku = it_cnt / NKV;     // buffer of this item, its earlier uses
+      unsigned char* bK = sK + kb * Cfg::kOperand;
+      unsigned char* bV = sV + kb * Cfg::kOperand;
+      if (ku >= 1) mbar_wait(&bars->k_free[kb], (ku - 1) & 1, wc, 4);
       if (lane == 0) {
-        mbar_expect_tx(&bars->k_full, Cfg::kOperand);
-        for (int s = 0; s < Cfg::kSubs; ++s) tma_load_3d_hint(sK + s * kSub, &k_map, &bars->k_full, s * 64, kvh, tok0, keep);
+        mbar_expect_tx(&bars->k_full[kb], Cfg::kOperand);
+        for (int s = 0; s < Cfg::kSubs; ++s) tma_load_3d_hint(bK + s * kSub, &k_map, &bars->k_full[kb], s * 64, kvh, tok0, keep);
       }
-      if (it_cnt >= 1) mbar_wait(&bars->v_free, (it_cnt - 1) & 1, wc, 5);
+      if (ku >= 1) mbar_wait(&bars->v_free[kb], (ku - 1) & 1, wc, 5);
       if (lane == 0) {
-        mbar_expect_tx(&bars->v_full, Cfg::kOperand);
-        for (int s = 0; s < Cfg::kSubs; ++s) tma_load_3d_hint(sV + s * kSub, &v_map, &bars->v_full, s * 64, kvh, tok0, keep);
+        mbar_expect_tx(&bars->v_full[kb], Cfg::kOperand);
+        for (int s = 0; s < Cfg::kSubs; ++s) tma_load_3d_hint(bV + s * kSub, &v_map, &bars->v_full[kb], s * 64, kvh, tok0, keep);
       }
       if (c.keys < kTile) {
         const int dead = kTile - c.keys;
-        mbar_wait(&bars->k_full, it_cnt & 1, wc, 7);
+        mbar_wait(&bars->k_full[kb], ku & 1, wc, 7);
         for (int i = lane; i < dead * 8 * Cfg::kSubs; i += 32) {
           const int s = i / (dead * 8), rr = c.keys + (i % (dead * 8)) / 8, ch = i % 8;
-          *reinterpret_cast<uint4*>(sK + s * kSub + rr * 128 + ch * 16) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(bK + s * kSub + rr * 128 + ch * 16) = make_uint4(0, 0, 0, 0);
         }
         fence_proxy_async();
         mbar_arrive_warp(&bars->k_fix);
-        mbar_wait(&bars->v_full, it_cnt & 1, wc, 8);
+        mbar_wait(&bars->v_full[kb], ku & 1, wc, 8);
         for (int i = lane; i < dead * 8 * Cfg::kSubs; i += 32) {
           const int s = i / (dead * 8), rr = c.keys + (i % (dead * 8)) / 8, ch = i % 8;
-          *reinterpret_cast<uint4*>(sV + s * kSub + rr * 128 + ch * 16) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(bV + s * kSub + rr * 128 + ch * 16) = make_uint4(0, 0, 0, 0);
         }
         fence_proxy_async();
         mbar_arrive_warp(&bars->v_fix);
@@ -559,9 +581,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       bars->cols[it_cnt & 7].n = -1;                          // end of the stream
       mbar_arrive(&bars->col_full[it_cnt & 7]);
       // No load may be in flight into this CTA's shared memory when it exits.
-      if (it_cnt >= 1) {
-        mbar_wait_quiet(&bars->k_full, (it_cnt - 1) & 1);
-        mbar_wait_quiet(&bars->v_full, (it_cnt - 1) & 1);
+      for (uint32_t back = 1; back <= (uint32_t)NKV && back <= it_cnt; ++back) {
+        const uint32_t n = it_cnt - back;
+        mbar_wait_quiet(&bars->k_full[n % NKV], (n / NKV) & 1);
+        mbar_wait_quiet(&bars->v_full[n % NKV], (n / NKV) & 1);
       }
     }
     __syncwarp();

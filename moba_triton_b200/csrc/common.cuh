@@ -111,8 +111,8 @@ __device__ __forceinline__ size_t part_row(const moba_b200_problem& p, size_t b,
 // ---- launch table of the tensor-core kernels: one tile plan per head_dim ----
 // The kernels take their compile-time constants from this table, and moba_b200_launch_plan
 // reports it, so there is one place that says what runs. Shared memory decides the entries:
-// at head_dim 64 four tiles, three Q stages and double-buffered K/V fit beside the P
-// buffers; at 128 every operand is twice as large.
+// at head_dim 64 four tiles, four Q stages and double-buffered K/V fit beside the output
+// staging tiles; at 128 every operand is twice as large.
 struct TensorCorePlan {
   int head_dim;
   int fwd_tiles_in_flight, fwd_q_stages;
@@ -120,7 +120,7 @@ struct TensorCorePlan {
   int gate_slots, gate_step;
 };
 constexpr TensorCorePlan kTensorCorePlans[2] = {
-    {64, 4, 3, 2, 2, 16, 8},
+    {64, 4, 4, 2, 2, 16, 8},
     {128, 2, 2, 1, 1, 7, 4},
 };
 constexpr const TensorCorePlan& tensor_core_plan(int head_dim) { return kTensorCorePlans[head_dim == 64 ? 0 : 1]; }

@@ -203,7 +203,7 @@ def test_launch_plan_is_a_table_lookup_on_the_problem_record():
     cfg = moba.MoBAConfig(128, 8)
     target = launch_plan((1, 131072, 4, 64), 4, torch.bfloat16, cfg)
     assert target["gate_path"] == target["fwd_path"] == target["bwd_path"] == "tcgen05"
-    assert (target["fwd_tiles_in_flight"], target["fwd_q_stages"]) == (4, 3)
+    assert (target["fwd_tiles_in_flight"], target["fwd_q_stages"]) == (4, 4)
     assert (target["bwd_kv_buffers"], target["bwd_gather_stages"]) == (2, 2)
     assert (target["gate_slots"], target["gate_step"]) == (16, 8)
     assert (target["transpose_chunk_rows"], target["transpose_chunks"], target["scatter_warps"]) == (512, 256, 8)
