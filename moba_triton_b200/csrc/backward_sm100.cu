@@ -9,7 +9,7 @@
 //   P  = exp2(S c - lse), dS = P (dP - delta)   (512 threads, 32 columns each) -> smem, 16-bit
 //   dV += P^T dO          A P  (M-major)   B dO (N-major)   N D    -> TMEM [256,256+D)
 //   dK += dS^T Q          A dS (M-major)   B Q  (N-major)   N D    -> TMEM [256+D,256+2D)
-//   dQ  = dS K            A dS (K-major)   B K  (N-major)   N D    -> TMEM [0,D)  (over S)
+//   dQ  = dS K            A dS (from TMEM, written back over dP)   B K  (N-major)   N D    -> TMEM [0,D)  (over S)
 // dQ rows go to the (query, slot) partial buffer; a later pass sums the slots.
 //
 // Stands in for moba_bwd_kernel of the reference (src/moba/kernels/moba_bwd.py:215-394),
@@ -235,7 +235,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
           auto p_ds = [&](auto masked) {
 #pragma unroll
             for (int hc = 0; hc < 2; ++hc) {              // sixteen columns at a time: few live registers
-              uint32_t sv[16], pv[16];
+              uint32_t sv[16], pv[16], dsk[8];
               const int col0 = wq * 32 + hc * 16;
               tmem_ld16(tmem + lane_off + cS + col0, sv);
               tmem_ld16(tmem + lane_off + cDP + col0, pv);
@@ -258,8 +258,13 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
                 const uint32_t off = swz128(r, (wq & 1) * 4 + hc * 2 + g);
                 *reinterpret_cast<uint4*>(p_sub + off) = wp;
                 *reinterpret_cast<uint4*>(s_sub + off) = wd;
+                dsk[g * 4 + 0] = wd.x; dsk[g * 4 + 1] = wd.y; dsk[g * 4 + 2] = wd.z; dsk[g * 4 + 3] = wd.w;
               }
+              // dS also goes back to TMEM, over the dP columns this thread has just read: dQ = dS K
+              // takes it from there as operand A (keys [16 ks, +16) in the eight columns from 16 ks).
+              tmem_st8(tmem + lane_off + cDP + col0, dsk);
             }
+            tmem_st_wait();
           };
           if (all_open) p_ds(std::false_type{}); else p_ds(std::true_type{});
         }
@@ -421,8 +426,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
           // while they write dQ out.
           if (!Cfg::kOwnStage) issue_dv();
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {            // 16 keys per step
-            if (leader) umma_f16(tmem + cDQ, make_sdesc(aS + (ks >> 2) * kSub + (ks & 3) * 32, 16, 1024),
+          for (int ks = 0; ks < 8; ++ks) {            // 16 keys per step, dS from TMEM
+            if (leader) umma_f16_ts(tmem + cDQ, tmem + cDP + 16 * ks,
                      make_sdesc(aK + ks * 2048, kSub, 1024), id_dq, ks > 0);
           }
           if (leader) umma_commit(&bars->dq_full);
