@@ -184,8 +184,8 @@ def base_config(wl, total_tokens):
 # captures of one launch at [1,65536,4,64] (2 082 816 pairs). The traffic of these kernels is
 # per-pair partial rows, so a launch's traffic is this figure times the pairs it processes.
 DRAM_BYTES_PER_PAIR = {
-    "bwd_sm100_kernel": (299.4e6 + 294.8e6) / 2082816,
-    "fwd_sm100_kernel": (164.0e6 + 226.6e6) / 2082816,
+    "bwd_sm100_kernel": (295.4e6 + 291.0e6) / 2082816,
+    "fwd_sm100_kernel": (167.6e6 + 225.0e6) / 2082816,
     "gate_sm100_kernel": 33.8e6 / 2082816,
 }
 
