@@ -46,7 +46,7 @@ constexpr int kSub = kTile * 128;          // bytes of one [128 rows][64 elems] 
 template <int D> struct FwdCfg {
   static constexpr int kSubs = D / 64;                 // sub-tiles per operand along the head dim
   static constexpr int kOperand = kSubs * kSub;        // bytes of K, V or one Q stage
-  // Tiles in flight (TMEM / P buffers, softmax warpgroups).
+  // Tiles in flight (TMEM buffers, output staging tiles, softmax warpgroups).
   static constexpr int kBufs = tensor_core_plan(D).fwd_tiles_in_flight;
   // Q stages form a ring over the CTA's tile sequence (tile t lives in stage t mod kQStages);
   // shared memory has no room for one stage per buffer at head_dim 64.
