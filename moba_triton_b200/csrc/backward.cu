@@ -16,28 +16,34 @@ namespace moba {
 // ---------------------------------------------------------------------------
 // delta: one thread per 16-byte vector, shuffle-reduced across the row
 // ---------------------------------------------------------------------------
+// grid (row groups of one batch entry, batch). A row is (token s, head h) of batch entry b; the
+// division by the head count that separates the two is a multiplication by a reciprocal the
+// host prepared (exact for the 31-bit row numbers the launcher admits): generic 64-bit
+// divisions had made this streaming kernel instruction-bound.
 template <typename T>
 __global__ void __launch_bounds__(256)
 delta_kernel(const T* __restrict__ out, const T* __restrict__ dout, float* __restrict__ delta,
-             size_t n_rows, int tokens, int q_heads, int d) {
+             unsigned rows_per_batch, int tokens, int q_heads, int d, unsigned long long heads_recip, int heads_shift) {
   constexpr int EPV = 16 / sizeof(T);
   const int tpr = d / EPV;                        // threads per row: power of two, <= 32
-  const size_t gid = (size_t)blockIdx.x * 256 + threadIdx.x;
-  const size_t r = gid / tpr;                     // token-major row (b, s, h)
-  const int c = (int)(gid % tpr);
+  const unsigned gid = blockIdx.x * 256u + threadIdx.x;
+  const unsigned r = gid / (unsigned)tpr;         // row (s, h) of this batch entry; tpr is a power of two
+  const int c = (int)(gid % (unsigned)tpr);
+  const size_t b = blockIdx.y;
   float acc = 0.f;
-  if (r < n_rows) {
-    const uint4 a = *reinterpret_cast<const uint4*>(out + r * d + c * EPV);
-    const uint4 g = *reinterpret_cast<const uint4*>(dout + r * d + c * EPV);
+  if (r < rows_per_batch) {
+    const size_t at = (b * rows_per_batch + r) * (size_t)d + c * EPV;
+    const uint4 a = *reinterpret_cast<const uint4*>(out + at);
+    const uint4 g = *reinterpret_cast<const uint4*>(dout + at);
     const T* av = reinterpret_cast<const T*>(&a);
     const T* gv = reinterpret_cast<const T*>(&g);
 #pragma unroll
     for (int e = 0; e < EPV; ++e) acc = fmaf(Elem<T>::to_f(av[e]), Elem<T>::to_f(gv[e]), acc);
   }
   for (int o = tpr >> 1; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (r < n_rows && c == 0) {
-    const size_t h = r % q_heads, bs_ = r / q_heads;
-    const size_t s = bs_ % tokens, b = bs_ / tokens;
+  if (r < rows_per_batch && c == 0) {
+    const unsigned s = (unsigned)(((unsigned long long)r * heads_recip) >> heads_shift);   // r / q_heads
+    const unsigned h = r - s * (unsigned)q_heads;
     delta[(b * q_heads + h) * tokens + s] = acc;
   }
 }
@@ -47,15 +53,25 @@ int launch_delta(const moba_b200_problem& p, const void* out, const void* dout, 
   KernelTimer timer__("delta_kernel", st);
   const int epv = 16 / (int)dtype_size(p.dtype);
   const int tpr = p.head_dim / epv;
-  if (tpr > 32 || tpr < 1) {
+  if (tpr > 32 || tpr < 1 || (tpr & (tpr - 1))) {
     set_error("backward: head_dim %d unsupported for this dtype", p.head_dim);
     return MOBA_B200_EUNSUPPORTED;
   }
-  const size_t n_rows = (size_t)p.batch * p.tokens * p.q_heads;
-  const unsigned blocks = (unsigned)((n_rows * tpr + 255) / 256);
-  if (!blocks) return MOBA_B200_OK;
+  const unsigned long long rows_per_batch = (unsigned long long)p.tokens * p.q_heads;
+  if (rows_per_batch * tpr >= (1ull << 31) || p.batch > 65535) {
+    set_error("backward: %llu rows per batch entry (or batch %d) exceed the delta kernel's grid", rows_per_batch, p.batch);
+    return MOBA_B200_EUNSUPPORTED;
+  }
+  if (!rows_per_batch || !p.batch) return MOBA_B200_OK;
+  // r / q_heads == (r * recip) >> shift for every r < 2^31, with recip = ceil(2^shift / q_heads)
+  int log2h = 0;
+  while ((1u << log2h) < (unsigned)p.q_heads) ++log2h;
+  const int shift = 31 + log2h;
+  const unsigned long long recip = ((1ull << shift) + p.q_heads - 1) / p.q_heads;
+  const dim3 grid((unsigned)((rows_per_batch * tpr + 255) / 256), (unsigned)p.batch);
 #define MOBA_DELTA(T) \
-  delta_kernel<T><<<blocks, 256, 0, st>>>((const T*)out, (const T*)dout, delta, n_rows, p.tokens, p.q_heads, p.head_dim)
+  delta_kernel<T><<<grid, 256, 0, st>>>((const T*)out, (const T*)dout, delta, (unsigned)rows_per_batch, p.tokens, \
+                                        p.q_heads, p.head_dim, recip, shift)
   if (p.dtype == MOBA_B200_F32) MOBA_DELTA(float);
   else if (p.dtype == MOBA_B200_BF16) MOBA_DELTA(__nv_bfloat16);
   else MOBA_DELTA(__half);
