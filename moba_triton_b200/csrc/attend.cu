@@ -217,14 +217,18 @@ int launch_fwd_portable(const moba_b200_problem& p, const void* q, const void* k
 template <typename TP, typename TO>
 __global__ void __launch_bounds__(256)
 merge_kernel(const TP* __restrict__ part_o, const float* __restrict__ part_lse,
-             TO* __restrict__ out, float* __restrict__ lse_out, size_t n_rows, int tokens,
+             TO* __restrict__ out, float* __restrict__ lse_out, int tokens,
              int q_heads, int d, int slots, int win_begin, int win_rows) {
+  // grid (row groups of one (batch entry, head), heads, batch): no division anywhere (generic
+  // 64-bit divisions cost this streaming kernel more instructions than its sums)
   constexpr int EPV = 16 / sizeof(TP);
-  const int tpr = d / EPV;                                   // threads per row
-  const size_t gid = (size_t)blockIdx.x * 256 + threadIdx.x;
-  const size_t r = gid / tpr;                                // head-major row (b, h, s)
+  const unsigned tpr = (unsigned)(d / EPV);                  // threads per row, a power of two
+  const unsigned gid = blockIdx.x * 256u + threadIdx.x;
+  const unsigned row = gid / tpr;                            // row of the window
   const int c = (int)(gid % tpr);
-  if (r >= n_rows) return;
+  if (row >= (unsigned)win_rows) return;
+  const size_t h = blockIdx.y, b = blockIdx.z, bh = b * q_heads + h;
+  const size_t r = bh * win_rows + row;                      // head-major row (b, h, s) of the partials
   const float* ls = part_lse + r * slots;
   float mg = -INFINITY;
   for (int i = 0; i < slots; ++i) {
@@ -258,8 +262,7 @@ merge_kernel(const TP* __restrict__ part_o, const float* __restrict__ part_lse,
     }
   }
   const float inv = 1.f / wsum;                              // wsum == 0 -> NaN, as the reference
-  const size_t s = win_begin + r % win_rows, bh = r / win_rows;     // r walks the window's rows
-  const size_t h = bh % q_heads, b = bh / q_heads;
+  const size_t s = (size_t)win_begin + row;
   TO* dst = out + ((b * tokens + s) * q_heads + h) * (size_t)d + c * EPV;
   __align__(16) TO packed_out[EPV];
 #pragma unroll
@@ -272,16 +275,19 @@ merge_kernel(const TP* __restrict__ part_o, const float* __restrict__ part_lse,
 int launch_merge(const moba_b200_problem& p, const void* part_o, const float* part_lse,
                  void* out, float* lse, cudaStream_t st) {
   KernelTimer timer__("merge_kernel", st);
-  const size_t n_rows = (size_t)p.batch * p.q_heads * window_rows(p);
   const bool pf32 = p.part_f32 || p.dtype == MOBA_B200_F32;
   const int epv = pf32 ? 4 : 8;
   const int tpr = p.head_dim / epv;
-  const size_t threads = n_rows * tpr;
-  const unsigned blocks = (unsigned)((threads + 255) / 256);
-  if (blocks == 0) return MOBA_B200_OK;
+  const long long threads = (long long)window_rows(p) * tpr;
+  if (tpr < 1 || (tpr & (tpr - 1)) || threads >= (1ll << 31) || p.q_heads > 65535 || p.batch > 65535) {
+    set_error("merge: head_dim %d, %d heads or batch %d outside the kernel's grid", p.head_dim, p.q_heads, p.batch);
+    return MOBA_B200_EUNSUPPORTED;
+  }
+  if (threads == 0 || p.batch == 0) return MOBA_B200_OK;
+  const dim3 blocks((unsigned)((threads + 255) / 256), (unsigned)p.q_heads, (unsigned)p.batch);
 #define MOBA_MERGE(TP, TO)                                                                      \
   merge_kernel<TP, TO><<<blocks, 256, 0, st>>>((const TP*)part_o, part_lse, (TO*)out, lse,      \
-                                               n_rows, p.tokens, p.q_heads, p.head_dim, p.slots,      \
+                                               p.tokens, p.q_heads, p.head_dim, p.slots,        \
                                                p.win_begin, window_rows(p))
   if (p.dtype == MOBA_B200_F32) MOBA_MERGE(float, float);
   else if (p.dtype == MOBA_B200_BF16) { if (pf32) MOBA_MERGE(float, __nv_bfloat16); else MOBA_MERGE(__nv_bfloat16, __nv_bfloat16); }

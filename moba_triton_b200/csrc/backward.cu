@@ -270,14 +270,17 @@ int launch_bwd_portable(const moba_b200_problem& p, const void* q, const void* k
 template <typename T>
 __global__ void __launch_bounds__(256)
 dq_reduce_kernel(const T* __restrict__ dq_part, const float* __restrict__ part_lse,
-                 T* __restrict__ dq, size_t n_rows, int tokens, int q_heads, int d, int slots,
+                 T* __restrict__ dq, int tokens, int q_heads, int d, int slots,
                  int win_begin, int win_rows) {
+  // grid (row groups of one (batch entry, head), heads, batch): no division anywhere
   constexpr int EPV = 16 / sizeof(T);
-  const int tpr = d / EPV;
-  const size_t gid = (size_t)blockIdx.x * 256 + threadIdx.x;
-  const size_t r = gid / tpr;                     // head-major row (b, h, s)
+  const unsigned tpr = (unsigned)(d / EPV);       // threads per row, a power of two
+  const unsigned gid = blockIdx.x * 256u + threadIdx.x;
+  const unsigned row = gid / tpr;                 // row of the window
   const int c = (int)(gid % tpr);
-  if (r >= n_rows) return;
+  if (row >= (unsigned)win_rows) return;
+  const size_t h = blockIdx.y, b = blockIdx.z;
+  const size_t r = (b * q_heads + h) * win_rows + row;   // head-major row (b, h, s) of the partials
   float acc[EPV];
 #pragma unroll
   for (int e = 0; e < EPV; ++e) acc[e] = 0.f;
@@ -301,8 +304,7 @@ dq_reduce_kernel(const T* __restrict__ dq_part, const float* __restrict__ part_l
       for (int e = 0; e < EPV; ++e) acc[e] += Elem<T>::to_f(vals[e]);
     }
   }
-  const size_t s = win_begin + r % win_rows, bh = r / win_rows;     // r walks the window's rows
-  const size_t h = bh % q_heads, b = bh / q_heads;
+  const size_t s = (size_t)win_begin + row;
   __align__(16) T packed_out[EPV];
 #pragma unroll
   for (int e = 0; e < EPV; ++e) packed_out[e] = Elem<T>::from_f(acc[e]);
@@ -315,11 +317,15 @@ int launch_dq_reduce(const moba_b200_problem& p, const void* dq_part, const floa
   KernelTimer timer__("dq_reduce_kernel", st);
   const int epv = 16 / (int)dtype_size(p.dtype);
   const int tpr = p.head_dim / epv;
-  const size_t n_rows = (size_t)p.batch * p.q_heads * window_rows(p);
-  const unsigned blocks = (unsigned)((n_rows * tpr + 255) / 256);
-  if (!blocks) return MOBA_B200_OK;
+  const long long threads = (long long)window_rows(p) * tpr;
+  if (tpr < 1 || (tpr & (tpr - 1)) || threads >= (1ll << 31) || p.q_heads > 65535 || p.batch > 65535) {
+    set_error("backward: head_dim %d, %d heads or batch %d outside the dQ reduction's grid", p.head_dim, p.q_heads, p.batch);
+    return MOBA_B200_EUNSUPPORTED;
+  }
+  if (threads == 0 || p.batch == 0) return MOBA_B200_OK;
+  const dim3 blocks((unsigned)((threads + 255) / 256), (unsigned)p.q_heads, (unsigned)p.batch);
 #define MOBA_DQR(T) \
-  dq_reduce_kernel<T><<<blocks, 256, 0, st>>>((const T*)dq_part, part_lse, (T*)dq, n_rows, p.tokens, p.q_heads, p.head_dim, p.slots, \
+  dq_reduce_kernel<T><<<blocks, 256, 0, st>>>((const T*)dq_part, part_lse, (T*)dq, p.tokens, p.q_heads, p.head_dim, p.slots, \
                                               p.win_begin, window_rows(p))
   if (p.dtype == MOBA_B200_F32) MOBA_DQR(float);
   else if (p.dtype == MOBA_B200_BF16) MOBA_DQR(__nv_bfloat16);
