@@ -15,6 +15,9 @@
 //                        O = P V (M128 N=D K128) with P as operand A **from TMEM**; each
 //                        blocks on what its next tile needs, so a tile that becomes ready
 //                        is issued without a polling round
+//   movers   (head_dim 128 only: NB x 4 warps) copy the query rows of their warpgroup's next
+//                        tile in and the staged output rows of its previous tile out; at
+//                        head_dim 64 the softmax warps do both themselves (below)
 //   softmax  (NB x 4 warps; warpgroup w owns tiles t = w mod NB)
 //            - gathers the 128 query rows of its *next* tile with 16-byte asynchronous
 //              copies, issued between the two passes over the current tile's scores: a
@@ -60,7 +63,13 @@ template <int D> struct FwdCfg {
   static constexpr int kSmemData = 2 * kKvBufs * kOperand + kQStages * kOperand + kBufs * kStageBytes;
   static constexpr int kSmem = kSmemData + 1024 /*align*/ + 10240 /*barriers, row tables*/;
   static constexpr int kMmaWarp = 4 * kBufs, kPvWarp = kMmaWarp + 1, kLoadWarp = kMmaWarp + 2;
-  static constexpr int kThreads = (4 * kBufs + 3) * 32;
+  // With two tiles in flight the softmax warps are only eight, and copying the next tile's
+  // query rows in and this tile's output rows out took half of a tile's time on them. There a
+  // second set of warps ("movers", four per tile in flight) does both, beside the softmax warps.
+  static constexpr bool kMovers = (kBufs == 2);
+  static constexpr int kMoverWarp0 = kLoadWarp + 1;
+  static constexpr int kMoverWarps = 4;                // per tile in flight (six were slower: 0.55 vs 0.49 ms on one KV head of cfg3)
+  static constexpr int kThreads = (4 * kBufs + 3 + (kMovers ? kMoverWarps * kBufs : 0)) * 32;
 };
 
 struct Column {                            // one unit of work
@@ -73,6 +82,8 @@ struct Bars {
   uint64_t q_full[4];                      // per buffer: the warpgroup's gathered Q tile has landed
   uint64_t q_empty[4];                     // per stage: the S MMA that read it has retired
   uint64_t s_full[4], p_full[4], o_full[4], so_free[4];
+  uint64_t o_staged[2], stage_free[2];     // movers: a tile's output rows are staged / have left the staging tile
+  uint64_t sp_free[2];                     // head_dim 128: the S / P columns of a buffer are free (its P V has retired)
   uint64_t col_full[8];                    // column descriptors published by the loader
   uint64_t drain[2];                       // all MMAs of an issuing thread have completed
   uint32_t tmem_base;
@@ -85,14 +96,14 @@ struct Bars {
 // AND of a predicate over the 128 threads of a warpgroup (named barrier `id`). Every decision
 // that steers a warpgroup past one of its own barriers is taken through this, so that a wait
 // that gave up in some threads only can never leave the others alone at a barrier.
-__device__ __forceinline__ bool group_all(bool pred, int id) {
+__device__ __forceinline__ bool group_all(bool pred, int id, int threads = 128) {
   uint32_t r;
   asm volatile(
       "{\n\t.reg .pred p, q;\n\t"
       "setp.ne.u32 q, %1, 0;\n\t"
-      "bar.red.and.pred p, %2, 128, q;\n\t"
+      "bar.red.and.pred p, %2, %3, q;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(r) : "r"((uint32_t)pred), "r"(id) : "memory");
+      : "=r"(r) : "r"((uint32_t)pred), "r"(id), "r"(threads) : "memory");
   return r != 0;
 }
 
@@ -176,11 +187,14 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
     }
     mbar_init(&bars->k_fix, 1); mbar_init(&bars->v_fix, 1);
     for (int i = 0; i < 4; ++i) {
-      mbar_init(&bars->q_full[i], 4); mbar_init(&bars->q_empty[i], 1);
+      mbar_init(&bars->q_full[i], Cfg::kMovers ? Cfg::kMoverWarps : 4); mbar_init(&bars->q_empty[i], 1);
       mbar_init(&bars->s_full[i], 1); mbar_init(&bars->p_full[i], 4);
       mbar_init(&bars->o_full[i], 1); mbar_init(&bars->so_free[i], 4);
     }
     for (int i = 0; i < 8; ++i) mbar_init(&bars->col_full[i], 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->o_staged[i], 4); mbar_init(&bars->stage_free[i], Cfg::kMoverWarps); mbar_init(&bars->sp_free[i], 1);
+    }
     mbar_init(&bars->drain[0], 1); mbar_init(&bars->drain[1], 1);
     bars->abort = 0;
     fence_barrier_init();
@@ -195,12 +209,18 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
   const float cs = rsqrtf((float)D) * kLog2e;
   const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
 
-  if (warp < 4 * NB) {
-    // ================ gather + softmax + epilogue warpgroups ================
-    const int wg = warp >> 2;                         // owns tiles with t % NB == wg and buffer wg
-    const int r = (warp & 3) * 32 + lane;             // row of the tile == TMEM lane
-    const int bar_id = 2 + wg;                        // named barrier of this warpgroup
-    const uint32_t tbuf = tmem + ((uint32_t)((warp & 3) * 32) << 16) + wg * ((D == 64) ? 128 : 256);
+  const bool is_mover = Cfg::kMovers && warp >= Cfg::kMoverWarp0;
+  if (warp < 4 * NB || is_mover) {
+    // ================ gather + softmax + epilogue warpgroups (and their movers) ================
+    // warp group: four softmax warps, or kMoverWarps movers, of tile buffer wg
+    const int gwarps = is_mover ? Cfg::kMoverWarps : 4;
+    const int gw = is_mover ? warp - Cfg::kMoverWarp0 : warp;
+    const int wg = gw / gwarps;                       // owns tiles with t % NB == wg and buffer wg
+    const int gtid = (gw % gwarps) * 32 + lane;       // thread of the group
+    const int gthreads = gwarps * 32;
+    const int r = gtid;                               // row of the tile == TMEM lane (softmax warps; movers beyond 127 own no row)
+    const int bar_id = 2 + wg + (is_mover ? NB : 0);  // named barrier of this group
+    const uint32_t tbuf = tmem + ((uint32_t)((gtid >> 5 & 3) * 32) << 16) + wg * ((D == 64) ? 128 : 256);
     unsigned char* myO = sO + wg * Cfg::kStageBytes;            // staging of this warpgroup's output rows
     // TMEM columns of a buffer: scores [0, 128); P, 16-bit pairs, over [0, 64); O in [128 - D, 128)
     // at head_dim 64 and in a second 128 columns at head_dim 128.
@@ -219,7 +239,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
         if (!k.have) {
           bool ok = blocking ? mbar_wait(&bars->col_full[k.it & 7], (k.it >> 3) & 1, wc, 1)
                              : mbar_try_wait(&bars->col_full[k.it & 7], (k.it >> 3) & 1);
-          ok = group_all(ok, bar_id);
+          ok = group_all(ok, bar_id, gthreads);
           if (!ok) return blocking ? 0 : -1;
           k.c = bars->cols[k.it & 7];
           if (k.c.n < 0) return 0;
@@ -234,7 +254,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
     auto load_entry = [&](const Cur& k, int& row, int& head, int& slot) {
       const int e = (int)(k.t - k.t0) * kTile + r;
       row = head = slot = 0;
-      if (e < k.c.n) {
+      if (r < kTile && e < k.c.n) {
         const size_t o = (size_t)k.c.kv_row * ix.capacity + k.c.lo + e;
         row = ld_nc_pinned(ix.row_indices + o); head = ld_nc_pinned(ix.head_indices + o);
         slot = ld_nc_pinned(ix.slot_of_pair + o);
@@ -246,29 +266,83 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
     uint32_t n_gather = 0;
     const uint64_t keep = l2_policy_evict_last();
     auto gather = [&](const Cur& k, int row, int head) {
-      const bool live = (int)(k.t - k.t0) * kTile + r < k.c.n;
+      const bool live = r < kTile && (int)(k.t - k.t0) * kTile + r < k.c.n;
       int* tab = bars->q_row[wg][n_gather & 1];
       ++n_gather;
-      tab[r] = live ? (int)((k.c.b * p.tokens + row) * p.q_heads + head) : -1;
-      asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+      if (r < kTile) tab[r] = live ? (int)((k.c.b * p.tokens + row) * p.q_heads + head) : -1;
+      asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(gthreads) : "memory");
       const uint32_t qs = k.t % NQ, uq = k.t / NQ;
       if (uq >= 1) mbar_wait(&bars->q_empty[qs], (uq - 1) & 1, wc, 9);
       const uint32_t stage = smem_u32(sQ) + qs * Cfg::kOperand;
-      const int cc = r % CPR;
+      if constexpr (Cfg::kMovers && Cfg::kMoverWarps != 4) {   // any number of threads: a row's pieces on neighbouring threads
+        for (int j = gtid; j < kTile * CPR; j += gthreads) {
+          const int rr = j / CPR, cc = j % CPR;
+          const int ri = tab[rr];
+          cp_async16_hint(stage + (cc >> 3) * kSub + swz128(rr, cc & 7), q + (size_t)(ri < 0 ? 0 : ri) * D + cc * 8,
+                          ri < 0 ? 0u : 16u, keep);
+        }
+      } else {
+        const int cc = r % CPR;
 #pragma unroll
-      for (int pass = 0; pass < CPR; ++pass) {
-        const int rr = pass * RPP + r / CPR;
-        const int ri = tab[rr];
-        cp_async16_hint(stage + (cc >> 3) * kSub + swz128(rr, cc & 7), q + (size_t)(ri < 0 ? 0 : ri) * D + cc * 8,
-                        ri < 0 ? 0u : 16u, keep);
+        for (int pass = 0; pass < CPR; ++pass) {
+          const int rr = pass * RPP + r / CPR;
+          const int ri = tab[rr];
+          cp_async16_hint(stage + (cc >> 3) * kSub + swz128(rr, cc & 7), q + (size_t)(ri < 0 ? 0 : ri) * D + cc * 8,
+                          ri < 0 ? 0u : 16u, keep);
+        }
       }
       cp_async_commit();
+    };
+
+    // The staged 16-bit output rows of a tile -> global memory, eight or sixteen lanes per row.
+    auto store_rows = [&](bool ok) {
+      constexpr int CPRO = D / 8;                    // 16-byte chunks per output row
+      if constexpr (Cfg::kMovers && Cfg::kMoverWarps != 4) {
+        for (int j = gtid; j < kTile * CPRO; j += gthreads) {
+          const int rr = j / CPRO, cc = j % CPRO;
+          unsigned char* op = bars->out_ptr[wg][rr];
+          const uint4 w = *reinterpret_cast<const uint4*>(myO + (cc >> 3) * kSub + swz128(rr, cc & 7));
+          if (op != nullptr && ok) st_global_stream16(op + cc * 16, w);
+        }
+      } else {
+        constexpr int RPPO = 128 / CPRO;             // rows per pass of the warpgroup
+        const int cc = r % CPRO;
+#pragma unroll
+        for (int pass = 0; pass < CPRO; ++pass) {
+          const int rr = pass * RPPO + r / CPRO;
+          unsigned char* op = bars->out_ptr[wg][rr];
+          const uint4 w = *reinterpret_cast<const uint4*>(myO + (cc >> 3) * kSub + swz128(rr, cc & 7));
+          if (op != nullptr && ok) st_global_stream16(op + cc * 16, w);
+        }
+      }
     };
 
     Cur pf{0u, 0u, (uint32_t)wg, 0, false, Column{}};
     int n_row = 0, n_head = 0, n_slot = 0;
     bool more = locate(pf, true) == 1;
     if (more) load_entry(pf, n_row, n_head, n_slot);
+    if (is_mover) {
+      // ---- movers: copy the rows of this warpgroup's tiles in, a tile ahead of the softmax
+      // warps, and the staged output rows of the tile before out ----
+      for (uint32_t j = 0;; ++j) {
+        const bool have_tile = more;
+        if (have_tile) {
+          gather(pf, n_row, n_head);
+          cp_async_wait<0>();
+          fence_proxy_async();
+          mbar_arrive_warp(&bars->q_full[wg]);
+        }
+        if (j >= 1 && sizeof(TP) == 2) {
+          const bool ok = mbar_wait(&bars->o_staged[wg], (j - 1) & 1, wc, 10);
+          store_rows(ok);
+          mbar_arrive_warp(&bars->stage_free[wg]);
+        }
+        if (!have_tile) break;
+        pf.t += NB;
+        more = locate(pf, true) == 1;
+        if (more) load_entry(pf, n_row, n_head, n_slot);
+      }
+    } else {
     bool gathered = false;
     PHASE_CLOCK(ph);
     while (more) {
@@ -277,13 +351,14 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       const int row = n_row, head = n_head, slot = n_slot;
       const uint32_t u = cur.t / NB;                   // how often this buffer has been used before
       const bool live = (int)(cur.t - cur.t0) * kTile + r < c.n;
-      if (!gathered) {                                 // first tile, or its descriptor came late
+      if (!Cfg::kMovers && !gathered) {                // first tile, or its descriptor came late
         gather(cur, row, head);
         cp_async_wait<0>();
         fence_proxy_async();
         mbar_arrive_warp(&bars->q_full[wg]);
       }
       PHASE_ADD(wc, 10, ph);                           // late gather
+      TRACE(error_word, cur.t, 0);
       int jmax = c.keys - 1;
       if (p.causal && live && (row - c.bos) / kTile == c.blk) jmax = min(jmax, row - c.key0);
       // Away from the diagonal block and the ragged ends every row keeps all 128 keys; such
@@ -298,6 +373,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       const int nxt = locate(pf, false);
       if (nxt == 1) load_entry(pf, n_row, n_head, n_slot);
       PHASE_ADD(wc, 11, ph);                           // s_full wait, next tile located
+      TRACE(error_word, cur.t, 1);
 
       uint32_t v[32];
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -320,8 +396,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       const float m2 = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * cs;
 
       PHASE_ADD(wc, 12, ph);                           // first pass (row maximum)
-      if (nxt == 1) gather(pf, n_row, n_head);
+      TRACE(error_word, cur.t, 2);
+      if (!Cfg::kMovers && nxt == 1) gather(pf, n_row, n_head);
       PHASE_ADD(wc, 13, ph);                           // copies of the next tile issued
+      TRACE(error_word, cur.t, 3);
 
       float l4[4] = {0.f, 0.f, 0.f, 0.f};
       auto exp_pass = [&](auto masked) {
@@ -352,11 +430,13 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       if (all_open) exp_pass(std::false_type{}); else exp_pass(std::true_type{});
       const float l = (l4[0] + l4[1]) + (l4[2] + l4[3]);
       PHASE_ADD(wc, 14, ph);                           // second pass (exp, P)
-      if (nxt == 1) { cp_async_wait<0>(); fence_proxy_async(); }   // the next tile's rows have landed and are visible to the MMA
+      TRACE(error_word, cur.t, 4);
+      if (!Cfg::kMovers && nxt == 1) { cp_async_wait<0>(); fence_proxy_async(); }   // the next tile's rows have landed and are visible to the MMA
       tc_fence_before();
       mbar_arrive_warp(&bars->p_full[wg]);
-      if (nxt == 1) mbar_arrive_warp(&bars->q_full[wg]);
+      if (!Cfg::kMovers && nxt == 1) mbar_arrive_warp(&bars->q_full[wg]);
       PHASE_ADD(wc, 15, ph);                           // copies landed, fences, arrivals
+      TRACE(error_word, cur.t, 5);
 
       // ---- epilogue of the same tile: O sits in the first D columns of this buffer ----
       const float inv = 1.f / l;
@@ -366,6 +446,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       const bool o_ok = mbar_wait(&bars->o_full[wg], u & 1, wc, 3) && s_ok;
       tc_fence_after();
       PHASE_ADD(wc, 16, ph);                           // o_full wait
+      TRACE(error_word, cur.t, 6);
+      // the movers have taken the previous tile's rows out of the staging tile
+      if (Cfg::kMovers && sizeof(TP) == 2 && u >= 1) mbar_wait(&bars->stage_free[wg], (u - 1) & 1, wc, 11);
 #pragma unroll 1
       for (int ch = 0; ch < D / 32; ++ch) {
         tmem_ld32(tbuf + kOCol + ch * 32, v);
@@ -393,29 +476,27 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       tc_fence_before();
       mbar_arrive_warp(&bars->so_free[wg]);               // the TMEM buffer may be overwritten
       PHASE_ADD(wc, 17, ph);                           // O read and staged
+      TRACE(error_word, cur.t, 7);
       if (live && o_ok) st_global_stream_f32(part_lse + dst_row, m2 + log2f(l));
       if (sizeof(TP) == 2) {
         bars->out_ptr[wg][r] = (live && o_ok) ? reinterpret_cast<unsigned char*>(dst) : nullptr;
-        asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
-        constexpr int CPRO = D / 8;                  // 16-byte chunks per output row
-        constexpr int RPPO = 128 / CPRO;             // rows per pass of the warpgroup
-        const int cc = r % CPRO;
-#pragma unroll
-        for (int pass = 0; pass < CPRO; ++pass) {
-          const int rr = pass * RPPO + r / CPRO;
-          unsigned char* op = bars->out_ptr[wg][rr];
-          const uint4 w = *reinterpret_cast<const uint4*>(myO + (cc >> 3) * kSub + swz128(rr, cc & 7));
-          if (op != nullptr) st_global_stream16(op + cc * 16, w);
+        if constexpr (Cfg::kMovers) {
+          mbar_arrive_warp(&bars->o_staged[wg]);       // (releasing: the movers see the rows and the table)
+        } else {
+          asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+          store_rows(true);
+          asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");   // the staging tile may be written again
         }
-        asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");   // the staging tile may be written again
       }
       PHASE_ADD(wc, 18, ph);                           // partial rows stored
+      TRACE(error_word, cur.t, 8);
 
       if (nxt == 1) { gathered = true; continue; }
       if (nxt == 0) break;
       more = locate(pf, true) == 1;                    // the descriptor was not there in time
       if (more) load_entry(pf, n_row, n_head, n_slot);
       gathered = false;
+    }
     }
   }
   else if (warp == Cfg::kMmaWarp || warp == Cfg::kPvWarp) {
@@ -444,12 +525,15 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
             // ---- S = Q K^T of tile t ----
             const uint32_t qs = t % NQ;
             mbar_wait(&bars->q_full[b], u & 1, wc, 21);
-            if (u >= 1) mbar_wait(&bars->so_free[b], (u - 1) & 1, wc, 22);
+            // The buffer's columns: where O has columns of its own (head_dim 128) the scores of
+            // the next tile only wait for P V of the previous one, not for its O to be read out.
+            if (u >= 1) mbar_wait(D == 128 ? &bars->sp_free[b] : &bars->so_free[b], (u - 1) & 1, wc, 22);
             if (i == 0) {
               mbar_wait(&bars->k_full[kb], ku & 1, wc, 23);
               if (partial) mbar_wait(&bars->k_fix, pt & 1, wc, 23);
             }
             tc_fence_after();
+            TRACE(error_word, t, 0);
             const uint32_t qb = aQ + qs * Cfg::kOperand;
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks) {
@@ -457,24 +541,29 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
               umma_f16(tmem + b * kBufCols, make_sdesc(qb + o, 16, 1024), make_sdesc(aK + o, 16, 1024),
                        idesc_s | fbits, ks > 0);
             }
+            TRACE(error_word, t, 1);
             umma_commit(&bars->s_full[b]);
             umma_commit(&bars->q_empty[qs]);
             if (i == nt - 1) umma_commit(&bars->k_free[kb]);
           } else {
             // ---- O = P V of tile t ----
             mbar_wait(&bars->p_full[b], u & 1, wc, 24);
+            if (D == 128 && u >= 1) mbar_wait(&bars->so_free[b], (u - 1) & 1, wc, 24);   // the O columns have been read out
             if (i == 0) {
               mbar_wait(&bars->v_full[kb], ku & 1, wc, 25);
               if (partial) mbar_wait(&bars->v_fix, pt & 1, wc, 25);
             }
             tc_fence_after();
+            TRACE(error_word, t, 0);
             // operand A: P from TMEM, 16 keys (eight columns of 16-bit pairs) per step
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
               umma_f16_ts(tmem + b * kBufCols + kOCol, tmem + b * kBufCols + ks * 8,
                           make_sdesc(aV + ks * 2048, kSub, 1024), idesc_o | fbits, ks > 0);
             }
+            TRACE(error_word, t, 1);
             umma_commit(&bars->o_full[b]);
+            if (D == 128) umma_commit(&bars->sp_free[b]);
             if (i == nt - 1) umma_commit(&bars->v_free[kb]);
           }
         }
