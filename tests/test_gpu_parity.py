@@ -370,12 +370,20 @@ def test_non_causal_own_block(device, kernel_path):
     assert max_abs_error(out, truth) <= ATOL[torch.bfloat16]
 
 
-def test_float32_partials_option(device, kernel_path):
+@pytest.mark.parametrize("d,s", [(64, 1024), (128, 2048)], ids=["d64", "d128"])
+def test_float32_partials_option(d, s, device, kernel_path):
+    """float32 partial outputs leave the forward kernel by another route than 16-bit ones
+    (straight from registers, not through the staging tile and, at head_dim 128, not through
+    the mover warps): both must give the merged output of the oracle."""
     cfg = moba.MoBAConfig(128, 4)
-    q, k, v = _dev(*make_qkv((1, 1024, 2, 64), dtype=torch.bfloat16, seed=19), device=device)
-    a = moba.moba_forward(q, k, v, cfg)
-    b = moba.moba_forward(q, k, v, cfg, partials_dtype=torch.float32)
+    q, k, v = make_qkv((1, s, 4, d), dtype=torch.bfloat16, seed=19, hkv=2)
+    qd, kd, vd = _dev(q, k, v, device=device)
+    a = moba.moba_forward(qd, kd, vd, cfg)
+    b = moba.moba_forward(qd, kd, vd, cfg, partials_dtype=torch.float32)
     assert max_abs_error(a, b) <= 2e-2
+    block_idx = moba.gate_select(qd, moba.pool_blocks(kd, cfg), cfg)
+    truth, _ = oracle_forward(q, k, v, cfg, block_idx)
+    assert max_abs_error(b, truth) <= ATOL[torch.bfloat16]
 
 
 def test_no_host_synchronisation_on_the_hot_path(device):
