@@ -115,8 +115,8 @@ __device__ __forceinline__ bool mbar_try_wait_sleep(uint64_t* bar, uint32_t pari
 // Waits for the phase with the given parity to complete. Returns false (and
 // latches the abort flag) if it gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, int site = 0) {
+  if (mbar_try_wait(bar, parity)) return true;        // already complete: no flag read, no clock read, no suspend hint
   if (*ctx.abort) return false;
-  if (mbar_try_wait(bar, parity)) return true;        // already complete: no clock read, no suspend hint
   const long long t0__ = clock64();
   for (;;) {
     if (mbar_try_wait_sleep(bar, parity)) {
