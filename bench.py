@@ -12,6 +12,7 @@ collective runs inside the op. Workloads:
            a global [1,131072,4N,64] problem with 4 heads per GPU)
   cfg2     [1,65536,4,64] per GPU
   gqa      q [1,131072,32,128], k/v 8 heads, KV heads sharded over the GPUs (strong scaling)
+  gqa1     one KV head of gqa with its four query heads (the shard of an 8-GPU run; for profiling)
   varlen   262144 packed tokens, 32 sequences, H=16, D=128, sequences sharded (strong scaling)
   skewed   q [1,524288,32,128], k/v 8 heads, selections concentrated on early blocks (strong)
   small    [1,8192,4,64], for quick checks and profiler captures
@@ -79,6 +80,13 @@ def describe(name, rank, world):
         return dict(name=name, seqlens=[s], hq=4, hkv=4, d=64, packed=False, scaling="weak",
                     seed=1000 * rank, skew=False,
                     text=f"[1,{s},4,64] bf16 per GPU (global [1,{s},{4 * world},64], heads sharded), "
+                         f"block {BLOCK}, top_k {TOPK}, fwd+bwd")
+    if name == "gqa1":
+        # one KV head of cfg3 with its four query heads: what each GPU holds when cfg3 is sharded
+        # over eight (small enough for a full ncu capture of the head_dim 128 kernels)
+        return dict(name=name, seqlens=[131072], hq=4, hkv=1, d=128, packed=False, scaling="weak",
+                    seed=1000 * rank, skew=False,
+                    text=f"q [1,131072,4,128] k/v 1 head bf16 per GPU (an eighth of cfg3), "
                          f"block {BLOCK}, top_k {TOPK}, fwd+bwd")
     if name in ("gqa", "skewed"):
         s = 131072 if name == "gqa" else 524288
